@@ -51,6 +51,7 @@ class KVGroupSpec:
     head_dim: int
     window: Optional[int] = None     # None: every key is kept; W: only the last W keys are read
     tensors: Optional[Tuple[object, ...]] = None
+    stride: int = 1                  # tokens per cache entry (P: one entry for every P tokens, e.g. pooled keys)
 
     def __post_init__(self):
         if self.tensors is None:
@@ -72,6 +73,7 @@ def _host():
         sig = {
             "pbe_cm_new": (vp, [i32, pi32, i32, pi32, i32, i32]),
             "pbe_cm_delete": (None, [vp]),
+            "pbe_cm_set_stride": (i32, [vp, i32, i32]),
             "pbe_cm_add_request": (i64, [vp]),
             "pbe_cm_is_live": (i32, [vp, i64]),
             "pbe_cm_num_live": (i32, [vp]),
@@ -167,6 +169,10 @@ class CacheManager:
         self._h = _host().pbe_cm_new(n, windows, self.page_tokens, pages, self.max_requests, 1 if lifo else 0)
         if not self._h:
             raise CacheError("the cache manager could not be created with these sizes")
+        for g, spec in enumerate(self.groups):
+            stride = int(getattr(spec, "stride", 1) or 1)
+            if stride != 1 and _host().pbe_cm_set_stride(self._h, g, stride) != 0:
+                raise CacheError(f"group {g}: a stride of {stride} tokens per entry cannot be set")
         self.pools = [PagePoolView(self, g) for g in range(n)]
         self._need = (ctypes.c_int * max(n, 1))()
         self.state_slot_assignments = 0
@@ -261,7 +267,8 @@ class CacheManager:
         """Tokens one request could hold with every page of the scarcest group."""
         if not self.groups:
             return 1 << 30
-        return min(p.num_pages for p in self.pools) * self.page_tokens
+        return min(p.num_pages * int(getattr(g, "stride", 1) or 1) for p, g in zip(self.pools, self.groups)) \
+            * self.page_tokens
 
     # ------------------------------------------------------------------ pages
     def reserve(self, handle: int, n_tokens: int) -> bool:
@@ -328,10 +335,11 @@ class CacheManager:
     def slot_of_token(self, handle: int, group: int, position: int) -> int:
         """page * page_tokens + offset of a token (infMain/source/base/sequence_kv_manager.cpp:41-52)."""
         table = self.block_table(handle, group)
-        page = table[position // self.page_tokens]
+        entry = position // int(getattr(self.groups[group], "stride", 1) or 1)
+        page = table[entry // self.page_tokens]
         if page == NO_PAGE:
             raise CacheError(f"position {position} lies in a page that was given back")
-        return page * self.page_tokens + position % self.page_tokens
+        return page * self.page_tokens + entry % self.page_tokens
 
     def page_generation(self, group: int, page: int) -> int:
         return _host().pbe_cm_page_generation(self._h, group, page)

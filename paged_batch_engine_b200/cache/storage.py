@@ -7,7 +7,7 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from ..parts.base import KVNeed, PagedNeed, StateNeed
+from ..parts.base import CompositeNeed, KVNeed, PagedNeed, StateNeed
 from .manager import CacheManager, KVGroupSpec
 
 
@@ -19,6 +19,7 @@ class LayerCache:
     tensors: Dict[str, torch.Tensor] = field(default_factory=dict)   # name -> [page, heads, page_tokens, width]
     state: Optional[torch.Tensor] = None  # [max_requests + 1, *shape] of a stateful mixer
     writes: bool = True
+    sub: Dict[str, "LayerCache"] = field(default_factory=dict)   # the parts of a ``CompositeNeed`` by name
 
     @property
     def k(self) -> Optional[torch.Tensor]:
@@ -48,27 +49,19 @@ class CacheStorage:
         self._layer_index: Dict[int, int] = {}
         self.state: Dict[int, torch.Tensor] = {}
         self.max_requests = int(max_requests)
+        # a composite need is taken apart: each of its parts gets a cache layer number of its own
+        # (beyond the model's), so that equal parts of different layers share pools like whole layers
+        self._parts: Dict[int, Dict[str, int]] = {}
+        self._next_layer = len(needs)
         for layer, need in enumerate(needs):
-            if isinstance(need, (KVNeed, PagedNeed)):
-                key = (tuple(need.tensors), need.window)
-                if not key[0]:
-                    raise TypeError(f"cache layer {layer}: a paged need lists at least one tensor")
-                if len({t.name for t in key[0]}) != len(key[0]):
-                    raise TypeError(f"cache layer {layer}: two cache tensors share a name")
-                if key not in members:
-                    members[key] = []
-                    keys.append(key)
-                self._layer_group[layer] = keys.index(key)
-                self._layer_index[layer] = len(members[key])
-                members[key].append(layer)
-            elif isinstance(need, StateNeed):
-                # one row per request slot and one more, which the padding rows of captured
-                # decode steps point at
-                self.state[layer] = torch.zeros((self.max_requests + 1,) + tuple(need.shape), dtype=need.dtype,
-                                                device=device)
-            elif need is not None:
-                raise TypeError(f"cache layer {layer}: unknown need {need!r}")
-        groups = [KVGroupSpec(tuple(members[k]), k[0][0].heads, k[0][0].width, k[1], tensors=k[0]) for k in keys]
+            self._place(layer, need, keys, members)
+        groups = [KVGroupSpec(tuple(members[k]), k[0][0].heads, k[0][0].width, k[1], tensors=k[0], stride=k[2])
+                  for k in keys]
+        if isinstance(num_pages, int):
+            # a group of one entry per `stride` tokens needs that much fewer pages for the same tokens,
+            # and at most one page more per request for its last, partly covered page
+            num_pages = [num_pages if g.stride == 1 else -(-num_pages // g.stride) + self.max_requests
+                         for g in groups]
         self.manager = CacheManager(groups, page_tokens, num_pages if groups else [], max_requests,
                                     lifo=lifo)
         self.paged: List[Dict[str, torch.Tensor]] = []
@@ -81,6 +74,34 @@ class CacheStorage:
                     x.fill_(float("nan"))
                 held[t.name] = x
             self.paged.append(held)
+
+    def _place(self, layer: int, need, keys, members) -> None:
+        if isinstance(need, CompositeNeed):
+            self._parts[layer] = {}
+            for name, part in need.parts:
+                sub_layer = self._next_layer
+                self._next_layer += 1
+                self._parts[layer][name] = sub_layer
+                self._place(sub_layer, part, keys, members)
+        elif isinstance(need, (KVNeed, PagedNeed)):
+            key = (tuple(need.tensors), need.window, int(getattr(need, "stride", 1) or 1))
+            if not key[0]:
+                raise TypeError(f"cache layer {layer}: a paged need lists at least one tensor")
+            if len({t.name for t in key[0]}) != len(key[0]):
+                raise TypeError(f"cache layer {layer}: two cache tensors share a name")
+            if key not in members:
+                members[key] = []
+                keys.append(key)
+            self._layer_group[layer] = keys.index(key)
+            self._layer_index[layer] = len(members[key])
+            members[key].append(layer)
+        elif isinstance(need, StateNeed):
+            # one row per request slot and one more, which the padding rows of captured
+            # decode steps point at
+            self.state[layer] = torch.zeros((self.max_requests + 1,) + tuple(need.shape), dtype=need.dtype,
+                                            device=self.device)
+        elif need is not None:
+            raise TypeError(f"cache layer {layer}: unknown need {need!r}")
 
     @property
     def groups(self):
@@ -105,6 +126,9 @@ class CacheStorage:
             t.index_fill_(0, idx, 0)
 
     def layer(self, cache_layer: int, writes: bool = True) -> LayerCache:
+        if cache_layer in self._parts:
+            return LayerCache(layer=cache_layer, writes=writes,
+                              sub={name: self.layer(l, writes) for name, l in self._parts[cache_layer].items()})
         if cache_layer in self._layer_group:
             g, i = self._layer_group[cache_layer], self._layer_index[cache_layer]
             return LayerCache(layer=cache_layer, group=g, tensors={n: t[i] for n, t in self.paged[g].items()},

@@ -45,9 +45,11 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_name_of(config_dict: Dict[str, Any]) -> str:
     archs = config_dict.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json has no 'architectures' list")
-    return str(archs[0])
+    if archs and isinstance(archs, (list, tuple)):
+        return str(archs[0])
+    if isinstance(config_dict.get("architecture"), str):      # some configurations name it in one string
+        return config_dict["architecture"]
+    raise ConfigError("config.json has no 'architectures' list (nor an 'architecture' name)")
 
 
 def load_config(path_or_dict):

@@ -29,11 +29,12 @@ class BlockSpec:
     parts themselves, and the prefix of its tensors in the checkpoint."""
     kind: str                      # arrangement, e.g. "prenorm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]           # None: the layer has no feed-forward
     norm_mixer: PartSpec
-    norm_feed_forward: PartSpec
+    norm_feed_forward: Optional[PartSpec]
     prefix: str                    # e.g. "model.layers.3."
     names: Dict[str, str] = field(default_factory=dict)  # sub-prefixes inside the block
+    args: Dict[str, Any] = field(default_factory=dict)   # constants of the arrangement itself (e.g. streams)
 
 
 @dataclass(frozen=True)
@@ -63,6 +64,7 @@ class ModelSpec:
     lm_head_name: Optional[str]    # None: the head is the embedding table (tied)
     max_position: int
     eos_token_ids: Tuple[int, ...] = ()
+    residual_streams: int = 1      # parallel residual streams (all start as the embedding, summed at the end)
 
     @property
     def num_cache_layers(self) -> int:

@@ -83,6 +83,7 @@ struct Request {
 struct Manager {
   int page_tokens = 0, max_requests = 0;
   std::vector<int> windows;               // -1: keep every key
+  std::vector<int> strides;               // tokens per cache entry of the group (1: an entry a token)
   std::vector<Pool> pools;
   std::vector<Request> slots;
   std::vector<int64_t> slot_generation;
@@ -97,7 +98,10 @@ struct Manager {
     if (!r.live || r.generation != gen) return nullptr;
     return &r;
   }
-  int64_t blocks_for(int64_t tokens) const { return (tokens + page_tokens - 1) / page_tokens; }
+  // pages of group g that n tokens need: the group holds one entry for every strides[g] tokens
+  // (entry e stands for tokens e*stride .. e*stride+stride-1 and exists once one of them does)
+  int64_t entries_for(int64_t tokens, size_t g) const { return (tokens + strides[g] - 1) / strides[g]; }
+  int64_t blocks_for(int64_t tokens, size_t g) const { return (entries_for(tokens, g) + page_tokens - 1) / page_tokens; }
 };
 }  // namespace
 
@@ -112,6 +116,7 @@ API void* pbe_cm_new(int n_groups, const int* windows, int page_tokens, const in
   m->page_tokens = page_tokens;
   m->max_requests = max_requests;
   m->windows.assign(windows, windows + n_groups);
+  m->strides.assign(n_groups, 1);
   m->pools.resize(n_groups);
   for (int g = 0; g < n_groups; ++g) {
     Pool& p = m->pools[g];
@@ -129,6 +134,16 @@ API void* pbe_cm_new(int n_groups, const int* windows, int page_tokens, const in
   return m;
 }
 API void pbe_cm_delete(void* h) { delete static_cast<Manager*>(h); }
+// Tokens per cache entry of a group (a group of pooled entries holds one for every `stride`
+// tokens); set before the first request, 1 by default.
+API int pbe_cm_set_stride(void* h, int g, int stride) {
+  Manager* m = static_cast<Manager*>(h);
+  if (g < 0 || g >= (int)m->pools.size() || stride <= 0) return kBadArg;
+  for (const Request& r : m->slots)
+    if (r.live) return kBadArg;
+  m->strides[g] = stride;
+  return kOk;
+}
 
 API int64_t pbe_cm_add_request(void* h) {
   Manager* m = static_cast<Manager*>(h);
@@ -179,9 +194,8 @@ API int pbe_cm_pages_needed(void* h, int64_t handle, int64_t n, int* out) {
   Manager* m = static_cast<Manager*>(h);
   Request* r = m->lookup(handle);
   if (!r) return kStale;
-  const int64_t target = m->blocks_for(r->reserved + n);
   for (size_t g = 0; g < m->pools.size(); ++g)
-    out[g] = (int)std::max<int64_t>(0, target - (int64_t)r->tables[g].size());
+    out[g] = (int)std::max<int64_t>(0, m->blocks_for(r->reserved + n, g) - (int64_t)r->tables[g].size());
   return kOk;
 }
 API int64_t pbe_cm_max_appendable(void* h, int64_t handle) {
@@ -191,8 +205,8 @@ API int64_t pbe_cm_max_appendable(void* h, int64_t handle) {
   if (m->pools.empty()) return (int64_t)1 << 30;
   int64_t best = INT64_MAX;
   for (size_t g = 0; g < m->pools.size(); ++g) {
-    const int64_t room = (int64_t)r->tables[g].size() * m->page_tokens - r->reserved +
-                         (int64_t)m->pools[g].free_q.size() * m->page_tokens;
+    const int64_t room = ((int64_t)r->tables[g].size() + (int64_t)m->pools[g].free_q.size()) * m->page_tokens *
+                             m->strides[g] - r->reserved;
     best = std::min(best, room);
   }
   return std::max<int64_t>(0, best);
@@ -203,12 +217,12 @@ API int pbe_cm_reserve(void* h, int64_t handle, int64_t n) {
   Request* r = m->lookup(handle);
   if (!r) return kStale;
   if (n < 0) return kBadArg;
-  const int64_t target = m->blocks_for(r->reserved + n);
   for (size_t g = 0; g < m->pools.size(); ++g) {
-    const int64_t need = target - (int64_t)r->tables[g].size();
+    const int64_t need = m->blocks_for(r->reserved + n, g) - (int64_t)r->tables[g].size();
     if (need > (int64_t)m->pools[g].free_q.size()) return 0;
   }
   for (size_t g = 0; g < m->pools.size(); ++g) {
+    const int64_t target = m->blocks_for(r->reserved + n, g);
     while ((int64_t)r->tables[g].size() < target) {
       const int page = m->pools[g].allocate(handle);
       if (page < 0) return kCorrupt;
@@ -227,7 +241,7 @@ API int pbe_cm_commit(void* h, int64_t handle, int64_t n) {
   for (size_t g = 0; g < m->pools.size(); ++g) {
     const int w = m->windows[g];
     if (w < 0) continue;
-    const int64_t first_needed = r->computed - w + 1;
+    const int64_t first_needed = (r->computed - w + 1) / m->strides[g];      // first entry still read
     if (first_needed <= 0) continue;
     const int64_t dead = std::min<int64_t>(first_needed / m->page_tokens, (int64_t)r->tables[g].size());
     for (int64_t b = r->first_live[g]; b < dead; ++b) {
@@ -246,11 +260,11 @@ API int pbe_cm_truncate(void* h, int64_t handle, int64_t n) {
   Request* r = m->lookup(handle);
   if (!r) return kStale;
   if (n < 0 || n > r->reserved) return kBadArg;
-  const int64_t keep = m->blocks_for(n);
   for (size_t g = 0; g < m->pools.size(); ++g)
-    if (keep < r->first_live[g]) return kBadArg;
+    if (m->blocks_for(n, g) < r->first_live[g]) return kBadArg;
   for (size_t g = 0; g < m->pools.size(); ++g) {
     auto& t = r->tables[g];
+    const int64_t keep = m->blocks_for(n, g);
     while ((int64_t)t.size() > keep) {
       const int page = t.back();
       t.pop_back();
@@ -321,8 +335,8 @@ API int pbe_cm_check(void* h, char* buf, int cap) {
   for (const Request& r : m->slots) {
     if (!r.live || !msg.empty()) continue;
     if (r.computed < 0 || r.computed > r.reserved) msg = "computed/reserved out of order";
-    for (const auto& t : r.tables)
-      if ((int64_t)t.size() != m->blocks_for(r.reserved)) msg = "a block table does not cover the reservation";
+    for (size_t g = 0; g < r.tables.size(); ++g)
+      if ((int64_t)r.tables[g].size() != m->blocks_for(r.reserved, g)) msg = "a block table does not cover the reservation";
   }
   if (msg.empty()) return 0;
   if (buf != nullptr && cap > 0) {
@@ -390,9 +404,10 @@ API int pbe_cm_decode_fill(void* h, int R, const int64_t* handles, int64_t* ctx_
       const int lo = (refresh || m->windows[g] >= 0) ? 0 : std::min(k, n);
       for (int i = lo; i < n; ++i) row[i] = t[i];
       k = n;
-      const int64_t blk = pos / P;
+      const int64_t entry = pos / m->strides[g];
+      const int64_t blk = entry / P;
       if (blk >= n || t[blk] < 0) return kBadArg;
-      slots[g][r] = (int32_t)((int64_t)t[blk] * P + pos % P);
+      slots[g][r] = (int32_t)((int64_t)t[blk] * P + entry % P);
     }
   }
   return kOk;

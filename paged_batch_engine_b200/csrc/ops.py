@@ -149,6 +149,225 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+# ------------------------------------------------------------------ residual streams, norms of branches
+def stream_norm(streams: torch.Tensor, y: Optional[torch.Tensor], mix: torch.Tensor, beta: torch.Tensor,
+                alpha: torch.Tensor, gain: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None, rms: bool = False) -> torch.Tensor:
+    """Folds the pending sublayer output ``y`` into the residual streams (float32 [T, S, W], in
+    place: r'_j = sum_s mix[s, j] r_s + beta[j] y), collapses them with ``alpha`` and writes the
+    LayerNorm (``gain``, ``bias``) or RMSNorm (``rms``) of the collapsed rows to ``out``.  With
+    ``rows`` (int32 [n]) output row i is made from batch row rows[i] and the streams are left
+    alone.  ``y`` None: nothing is folded in."""
+    _need_cuda(streams, y, mix, beta, alpha, gain, bias, out, rows)
+    _need_contiguous(streams, y, mix, beta, alpha, gain, bias, out, rows)
+    if streams.dtype != torch.float32 or streams.dim() != 3:
+        raise KernelError("stream_norm: the residual streams are float32 [T, S, W]")
+    T, S, W = streams.shape
+    n = out.shape[0]
+    for name, t, size in (("mix", mix, S * S), ("beta", beta, S), ("alpha", alpha, S), ("gain", gain, W)):
+        if t.dtype != torch.float32 or t.numel() != size:
+            raise KernelError(f"stream_norm: {name} must be float32 with {size} elements")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != W):
+        raise KernelError("stream_norm: bias must be float32 [W]")
+    if out.shape[-1] != W or (y is not None and tuple(y.shape) != (T, W)):
+        raise KernelError("stream_norm: shapes do not agree")
+    if rows is None and n != T:
+        raise KernelError("stream_norm: output rows do not match the batch")
+    if rows is not None and (rows.dtype != torch.int32 or rows.numel() != n):
+        raise KernelError("stream_norm: rows must be int32, one per output row")
+    if S > 8 or W * 4 > 200 * 1024:
+        raise KernelError(f"stream_norm takes at most 8 streams and rows of at most 51,200 floats (got {S}, {W})")
+    fn = _fn("streams", "pbe_stream_norm",
+             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+              c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_ptr(streams), _ptr(y), _dtype_code(y) if y is not None else F32, _ptr(mix), _ptr(beta), _ptr(alpha),
+              _ptr(gain), _ptr(bias), _ptr(out), _dtype_code(out), _ptr(rows), n, S, W, float(eps),
+              1 if rms else 0, _stream()), "stream_norm")
+    return out
+
+
+def branch_rms_mean(branches, gains, eps: float) -> torch.Tensor:
+    """mean over the branches of x_b / rms(x_b) * gain_b, row by row; up to four branches of
+    equal shape [T, W] and dtype; gains float32 [W]."""
+    n = len(branches)
+    if not 1 <= n <= 4 or len(gains) != n:
+        raise KernelError("branch_rms_mean takes one to four branches and a gain for each")
+    _need_cuda(*branches, *gains)
+    _need_contiguous(*branches, *gains)
+    T, W = branches[0].shape
+    for x, g in zip(branches, gains):
+        if x.shape != (T, W) or x.dtype != branches[0].dtype or g.dtype != torch.float32 or g.numel() != W:
+            raise KernelError("branch_rms_mean: shapes or dtypes do not agree")
+    out = torch.empty_like(branches[0])
+    xs = (c_void_p * 4)(*[x.data_ptr() for x in branches])
+    gs = (c_void_p * 4)(*[g.data_ptr() for g in gains])
+    fn = _fn("streams", "pbe_branch_rms_mean", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                                                c_void_p])
+    _check(fn(ctypes.addressof(xs), ctypes.addressof(gs), n, _ptr(out), _dtype_code(out), T, W, float(eps),
+              _stream()), "branch_rms_mean")
+    return out
+
+
+def gated_rms(o: torch.Tensor, gate: torch.Tensor, gain: Optional[torch.Tensor], heads: int, eps: float,
+              per_head: bool, gate_act: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """out = o / rms(o) (* gain) * act(gate): ``o`` float32 [T, heads * E]; the root mean square
+    over the whole row or over each head's E values; ``gate`` a column slice [T, heads * E] of a
+    wider matrix (unit column stride); ``gate_act`` "sigmoid" or "silu"."""
+    _need_cuda(o, gate, gain)
+    _need_contiguous(o, gain)
+    T, N = o.shape
+    if o.dtype != torch.float32 or N % heads or tuple(gate.shape) != (T, N) or gate.stride(1) != 1:
+        raise KernelError("gated_rms: shapes, strides or dtypes do not agree")
+    if gate.dtype != out_dtype:
+        raise KernelError("gated_rms: the gate has the output's dtype")
+    if gain is not None and (gain.dtype != torch.float32 or gain.numel() != N):
+        raise KernelError("gated_rms: gain must be float32 [heads * E]")
+    if gate_act not in ("sigmoid", "silu"):
+        raise KernelError(f"gated_rms: unknown gate activation {gate_act!r}")
+    out = torch.empty((T, N), dtype=out_dtype, device=o.device)
+    fn = _fn("streams", "pbe_gated_rms", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_float, c_int, c_int, c_void_p])
+    _check(fn(_ptr(o), _ptr(gate), gate.stride(0) if T > 1 else N, _ptr(gain), _ptr(out), _dtype_code(out), T, heads,
+              N // heads, float(eps), 1 if per_head else 0, 1 if gate_act == "silu" else 0, _stream()), "gated_rms")
+    return out
+
+
+# ------------------------------------------------------------------ linear attention (decayed recurrence)
+def _column_slice(x: torch.Tensor, what: str):
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError(f"{what}: operands are column slices of a row-major matrix")
+
+
+def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
+                     q_start: torch.Tensor, q_len: torch.Tensor, slots: torch.Tensor, num_requests: int,
+                     heads: int, k_scale: float = 1.0, silu: bool = False) -> torch.Tensor:
+    """o_t = S_t^T q_t with S_t = decay_h S_{t-1} + k_t v_t^T per head, request by request over
+    the rows each brings (``q_start``, ``q_len`` int32 [R]); ``state`` float32 [slots, H, D, E]
+    is read at ``slots[r]`` and left updated.  q, k [T, H*D] and v [T, H*E] are column slices of
+    one projection matrix (equal row stride).  Returns float32 [T, H*E]."""
+    _need_cuda(q, k, v, state, decay, q_start, q_len, slots)
+    for x in (q, k, v):
+        _column_slice(x, "linear_attention")
+    T = q.shape[0]
+    ld = q.stride(0) if T > 1 else max(q.stride(0), q.shape[1])
+    if T > 1 and (k.stride(0) != ld or v.stride(0) != ld):
+        raise KernelError("linear_attention: q, k and v must share a row stride")
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise KernelError("linear_attention: q, k and v share a dtype")
+    D, E = q.shape[1] // heads, v.shape[1] // heads
+    if q.shape[1] != heads * D or k.shape[1] != heads * D or v.shape[1] != heads * E:
+        raise KernelError("linear_attention: widths are not multiples of the head count")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, D, E) or not state.is_contiguous():
+        raise KernelError("linear_attention: the state is float32 [slots, heads, D, E]")
+    if decay.dtype != torch.float32 or decay.numel() != heads:
+        raise KernelError("linear_attention: decay is float32 [heads]")
+    for x in (q_start, q_len, slots):
+        if x.dtype != torch.int32 or x.numel() < num_requests:
+            raise KernelError("linear_attention: request arrays are int32 [R]")
+    if D > 512:
+        raise KernelError(f"linear_attention: key width {D} per head is beyond 512")
+    out = torch.empty((T, heads * E), dtype=torch.float32, device=q.device)
+    fn = _fn("linear_attention", "pbe_linear_attention",
+             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_ptr(q), _ptr(k), _ptr(v), ld, _dtype_code(q), _ptr(out), _ptr(state), _ptr(decay), _ptr(q_start),
+              _ptr(q_len), _ptr(slots), num_requests, heads, D, E, float(k_scale), 1 if silu else 0, _stream()),
+           "linear_attention")
+    return out
+
+
+# ------------------------------------------------------------------ window + pooled blocks attention
+def qk_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_gain: Optional[torch.Tensor],
+               k_gain: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int,
+               positions: torch.Tensor, slots: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
+               v_pages: Optional[torch.Tensor], heads: int, kv_heads: int, eps: float, page_tokens: int) -> torch.Tensor:
+    """RMS norm over the whole query projection and over the whole key projection (gains float32,
+    None: no norm), rotary encoding of neighbouring pairs on the first ``rotary_dim`` dimensions of
+    every head, keys and values into the token pages; returns the queries [T, heads * D].
+    q, k, v are column slices of one projection matrix."""
+    _need_cuda(q, k, v, q_gain, k_gain, inv_freq, positions, slots, k_pages, v_pages)
+    for x in (q, k, v):
+        _column_slice(x, "qk_prepare")
+    T = q.shape[0]
+    D, E = q.shape[1] // heads, v.shape[1] // kv_heads
+    if q.shape[1] != heads * D or k.shape[1] != kv_heads * D or v.shape[1] != kv_heads * E or D % 2:
+        raise KernelError("qk_prepare: widths do not agree with the head counts (and the key width is even)")
+    ld = q.stride(0) if T > 1 else q.shape[1] + k.shape[1] + v.shape[1]
+    if T > 1 and (k.stride(0) != ld or v.stride(0) != ld):
+        raise KernelError("qk_prepare: q, k and v must share a row stride")
+    if positions.dtype != torch.int32 or positions.numel() != T:
+        raise KernelError("qk_prepare: positions must be int32 [T]")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rotary_dim
+                                 or rotary_dim > D):
+        raise KernelError("qk_prepare: inv_freq must be float32 [rotary_dim / 2], rotary_dim <= D")
+    if k_pages is not None:
+        if slots is None or slots.dtype != torch.int32 or slots.numel() != T:
+            raise KernelError("qk_prepare: slots must be int32 [T]")
+        if tuple(k_pages.shape[1:]) != (kv_heads, page_tokens, D) or tuple(v_pages.shape[1:]) != (kv_heads, page_tokens, E) \
+                or k_pages.dtype != q.dtype or v_pages.dtype != q.dtype:
+            raise KernelError("qk_prepare: pages must be [page, kv_head, page_tokens, width] in the activations' dtype")
+    q_out = torch.empty((T, heads * D), dtype=q.dtype, device=q.device)
+    fn = _fn("pooled_attention", "pbe_qk_prepare", [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 8 +
+             [c_int] * 7 + [c_float, c_int, c_void_p])
+    _check(fn(_ptr(q), _ptr(k), _ptr(v), ld, _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq), _ptr(positions), _ptr(slots),
+              _ptr(q_out), _ptr(k_pages), _ptr(v_pages), T, heads, kv_heads, D, E,
+              rotary_dim if inv_freq is not None else 0, page_tokens, float(eps), _dtype_code(q), _stream()),
+           "qk_prepare")
+    return q_out
+
+
+def pool_blocks(k_tok, v_tok, k_pool, v_pool, positions, request_of_row, bt_tok, bt_pool, pool: int,
+                page_tokens: int) -> None:
+    """For every row whose position closes a block of ``pool`` tokens: the means of the block's
+    keys and values, as the token pages hold them, into the block's entry of the pooled pages."""
+    _need_cuda(k_tok, v_tok, k_pool, v_pool, positions, request_of_row, bt_tok, bt_pool)
+    _need_contiguous(k_tok, v_tok, k_pool, v_pool, positions, request_of_row, bt_tok, bt_pool)
+    T = positions.numel()
+    G, D, E = k_tok.shape[1], k_tok.shape[3], v_tok.shape[3]
+    if tuple(k_pool.shape[1:]) != tuple(k_tok.shape[1:]) or tuple(v_pool.shape[1:]) != tuple(v_tok.shape[1:]) \
+            or k_tok.shape[2] != page_tokens or len({k_tok.dtype, v_tok.dtype, k_pool.dtype, v_pool.dtype}) != 1:
+        raise KernelError("pool_blocks: token pages and pooled pages differ in geometry or dtype")
+    fn = _fn("pooled_attention", "pbe_pool_blocks", [c_void_p] * 7 + [c_int, c_void_p] + [c_int] * 8 + [c_void_p])
+    _check(fn(_ptr(k_tok), _ptr(v_tok), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(request_of_row),
+              _ptr(bt_tok), bt_tok.shape[1], _ptr(bt_pool), bt_pool.shape[1], T, G, D, E, page_tokens, int(pool),
+              _dtype_code(k_tok), _stream()), "pool_blocks")
+
+
+def pooled_attention_tile_rows(heads: int, value_dim: int, want: int) -> int:
+    fn = _fn("pooled_attention", "pbe_pooled_attention_tile_rows", [c_int, c_int, c_int])
+    rows = fn(heads, value_dim, want)
+    if rows <= 0:
+        raise KernelError(f"pooled attention: {heads} heads x {value_dim} values a row are beyond the kernel")
+    return rows
+
+
+def pooled_attention(q, k_tok, v_tok, k_pool, v_pool, talk, tiles, num_tiles: int, tile_rows: int, q_start, q_len,
+                     seq_len, bt_tok, bt_pool, heads: int, kv_heads: int, scale: float, window: int, pool: int,
+                     page_tokens: int) -> torch.Tensor:
+    """Softmax attention of every row over the tokens of its window and the pooled blocks before
+    it (one softmax), the probabilities mixed across heads by ``talk`` (float32 [H, H], row h
+    weighs the heads' probabilities for head h; None: no mixing).  Returns [T, heads * E]."""
+    _need_cuda(q, k_tok, v_tok, k_pool, v_pool, talk, tiles, q_start, q_len, seq_len, bt_tok, bt_pool)
+    _need_contiguous(q, k_tok, v_tok, k_pool, v_pool, talk, tiles, q_start, q_len, seq_len, bt_tok, bt_pool)
+    T = q.shape[0]
+    D, E = k_tok.shape[3], v_tok.shape[3]
+    if q.shape[1] != heads * D or k_tok.shape[1] != kv_heads or k_tok.dtype != q.dtype or v_tok.dtype != q.dtype:
+        raise KernelError("pooled_attention: shapes or dtypes do not agree")
+    if talk is not None and (talk.dtype != torch.float32 or tuple(talk.shape) != (heads, heads)):
+        raise KernelError("pooled_attention: the mixing matrix is float32 [heads, heads]")
+    if pool and (k_pool is None or bt_pool is None):
+        raise KernelError("pooled_attention: pooled blocks need their pages and block table")
+    out = torch.empty((T, heads * E), dtype=q.dtype, device=q.device)
+    fn = _fn("pooled_attention", "pbe_pooled_attention",
+             [c_void_p] * 8 + [c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p, c_int] + [c_int] * 7 +
+             [c_float, c_int, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_tok), _ptr(v_tok), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(talk), _ptr(tiles),
+              num_tiles, tile_rows, _ptr(q_start), _ptr(q_len), _ptr(seq_len), _ptr(bt_tok), bt_tok.shape[1],
+              _ptr(bt_pool), bt_pool.shape[1] if bt_pool is not None else 0, heads, kv_heads, D, E, page_tokens,
+              int(window), int(pool or 0), float(scale), _dtype_code(q), _stream()), "pooled_attention")
+    return out
+
+
 # ------------------------------------------------------------------ rope + cache write
 def rope_kv_write(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],

@@ -275,6 +275,7 @@ class StepContext:
         i_qs, i_ql, i_sl = pk.add(q_start), pk.add(q_len), pk.add(seq_len)
         i_want = pk.add(np.array(want_rows, dtype=np.int64))
         i_state = pk.add(self.state_slots_host)
+        i_req = pk.add(req_of_tok)
         i_groups = []
         for g in range(len(manager.groups)):
             tables = [manager.block_table(e.handle, g) for e in entries]
@@ -282,11 +283,12 @@ class StepContext:
             bt = np.full((R, stride), -1, dtype=np.int32)
             for r, t in enumerate(tables):
                 bt[r, :len(t)] = t
-            blk = positions // P
-            page = bt[req_of_tok, blk]
+            # a group of one entry per `stride` tokens: the token's slot is its entry's
+            entry = positions // int(getattr(manager.groups[g], "stride", 1) or 1)
+            page = bt[req_of_tok, entry // P]
             if (page < 0).any():
                 raise ValueError("a token of this step lies in a page that is not held")
-            slots = page.astype(np.int64) * P + positions % P
+            slots = page.astype(np.int64) * P + entry % P
             i_groups.append((pk.add(bt), stride, pk.add(slots)))
         i_work = {}
         self._work_host = {}
@@ -309,6 +311,8 @@ class StepContext:
         self.q_start, self.q_len, self.seq_len = pk.view(i_qs), pk.view(i_ql), pk.view(i_sl)
         self.want_rows = pk.view(i_want)
         self.state_slots = pk.view(i_state)
+        self.request_of_row = pk.view(i_req)       # int32 [T]: which entry of the step a row belongs to
+        self._row_tiles: Dict[int, tuple] = {}
         self._groups = [GroupArrays(pk.view(ib), stride, pk.view(isl)) for ib, stride, isl in i_groups]
         self._work: Dict[tuple, AttentionWork] = {}
         for key, (iw, nw, itsr, ist, isc, ns, max_splits, (kinds, small_items)) in i_work.items():
@@ -324,6 +328,21 @@ class StepContext:
 
     def group(self, g: int) -> GroupArrays:
         return self._groups[g]
+
+    def row_tiles(self, tile_rows: int):
+        """(int32 [n, 3] on the device, n): the step's rows cut into tiles of at most ``tile_rows``
+        consecutive rows of one request: (request, first batch row, rows).  Made on first use."""
+        got = self._row_tiles.get(tile_rows)
+        if got is None:
+            tiles = []
+            for r, (qs, n) in enumerate(zip(self.q_start_host, self.q_len_host)):
+                for o in range(0, int(n), tile_rows):
+                    tiles.append((r, int(qs) + o, min(tile_rows, int(n) - o)))
+            host = torch.tensor(tiles, dtype=torch.int32)
+            if torch.cuda.is_available():
+                host = host.pin_memory()
+            got = self._row_tiles[tile_rows] = (host.to(self.device, non_blocking=True), len(tiles), host)
+        return got[0], got[1]
 
     def attention_work(self, group: int, group_size: int, tile_rows: int, window, num_heads: int,
                        head_dim: int) -> AttentionWork:

@@ -138,6 +138,9 @@ class DecoderModel:
         T = ctx.num_tokens
         residual = torch.empty((T, s.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(residual, self.embed, ctx.token_ids)
+        if s.residual_streams > 1:
+            # several residual streams, [T, S, W]: every one starts as the embedding
+            residual = residual.unsqueeze(1).expand(T, s.residual_streams, s.hidden_size).contiguous()
         delta = None
         native = self._native_descs(ctx)
         if native is not None:

@@ -1,12 +1,17 @@
-from .base import (Block, CacheTensor, FeedForward, KVNeed, Mixer, Norm, PagedNeed, Part, PositionEncoding, StateNeed,
+from .base import (Block, CacheTensor, CompositeNeed, FeedForward, KVNeed, Mixer, Norm, PagedNeed, Part, PositionEncoding, StateNeed,
                    build_block, build_part, register_part)
-from .norm import RMSNorm
+from .norm import LayerNorm, PendingUpdate, RMSNorm
 from .rope import NoPositionEncoding, RotaryEncoding
 from .attention import GQAttention
 from .mlp import SwiGLU
 from .block import PreNormBlock
+from .linear_attention import DecayLinearAttention
+from .pooled_attention import PooledWindowAttention
+from .parallel import ParallelMixer
+from .streams import StreamBlock, StreamConnection
 
-__all__ = ["Block", "CacheTensor", "FeedForward", "KVNeed", "Mixer", "Norm", "PagedNeed", "Part", "PositionEncoding",
+__all__ = ["Block", "CacheTensor", "CompositeNeed", "FeedForward", "KVNeed", "Mixer", "Norm", "PagedNeed", "Part", "PositionEncoding",
            "StateNeed",
            "build_block", "build_part", "register_part", "RMSNorm", "NoPositionEncoding", "RotaryEncoding",
-           "GQAttention", "SwiGLU", "PreNormBlock"]
+           "GQAttention", "SwiGLU", "PreNormBlock", "LayerNorm", "PendingUpdate", "DecayLinearAttention",
+           "PooledWindowAttention", "ParallelMixer", "StreamBlock", "StreamConnection"]

@@ -18,7 +18,7 @@ PositionEncoding: ``kernel_args() -> (inv_freq | None, rotary_dim, interleaved)`
             ``positions`` is int32 [rows]: the tokens' places in the sequence, or the position ids
             the step's entries brought (``StepEntry.position_ids``), then [rows, axes] when they
             have several axes.
-Mixer:      ``cache_need() -> KVNeed | PagedNeed | StateNeed | None`` (what it keeps between steps) and
+Mixer:      ``cache_need() -> KVNeed | PagedNeed | StateNeed | CompositeNeed | None`` (what it keeps between steps) and
             ``forward(x, ctx, cache) -> y`` over all rows of the step.
 FeedForward: ``forward(x, ctx) -> y``.
 Block:      ``forward(residual, delta, ctx, cache) -> (residual, delta)``: the arrangement
@@ -48,10 +48,13 @@ class CacheTensor:
 class PagedNeed:
     """What a mixer keeps per token, in pages: any number of named tensors, each with its own
     heads and width (keys and values of different widths, one compressed latent, ...), and how
-    long a token is kept (``window`` None: for ever; W: while one of the last W).  Layers with
-    equal needs share a page pool and a block table."""
+    long a token is kept (``window`` None: for ever; W: while one of the last W).  ``stride``
+    P > 1: the tensors hold one entry for every P tokens (entry e stands for tokens e*P ..
+    e*P+P-1, e.g. a pooled key and value), so a page covers ``page_tokens * P`` tokens.  Layers
+    with equal needs share a page pool and a block table."""
     tensors: Tuple[CacheTensor, ...]
     window: Optional[int] = None
+    stride: int = 1
 
 
 @dataclass(frozen=True)
@@ -77,6 +80,18 @@ class StateNeed:
     decode step point at it."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class CompositeNeed:
+    """What a mixer made of several parts keeps: its parts' needs by name (each a ``KVNeed``,
+    ``PagedNeed``, ``StateNeed``, another ``CompositeNeed`` or None).  The mixer finds them in
+    ``cache.sub[name]``, each a ``LayerCache`` of its own."""
+    parts: Tuple[Tuple[str, object], ...]
+
+    @staticmethod
+    def of(**parts) -> "CompositeNeed":
+        return CompositeNeed(tuple(parts.items()))
 
 
 class Part:

@@ -16,7 +16,9 @@ class SwiGLU(FeedForward):
     [hidden, inter]; ``tensor_names`` renames them, e.g. ``dict(gate="w1", down="w2", up="w3")``."""
     TENSOR_NAMES = dict(gate="gate_proj", up="up_proj", down="down_proj")
 
-    def __init__(self, hidden_size: int, intermediate_size: int, dtype, device, tensor_names=None):
+    def __init__(self, hidden_size: int, intermediate_size: int, dtype, device, tensor_names=None,
+                 weight_suffix: str = ".weight"):
+        self.suffix = weight_suffix      # what follows a projection's name in the checkpoint ("" for bare names)
         unknown = set(tensor_names or {}) - set(self.TENSOR_NAMES)
         if unknown:
             raise ValueError(f"tensor_names knows gate, up and down; got {sorted(unknown)}")
@@ -31,18 +33,18 @@ class SwiGLU(FeedForward):
     def param_specs(self, prefix):
         i, h = self.intermediate_size, self.hidden_size
         n = self.names
-        return [ParamSpec(prefix + n["gate"] + ".weight", (i, h)),
-                ParamSpec(prefix + n["up"] + ".weight", (i, h)),
-                ParamSpec(prefix + n["down"] + ".weight", (h, i))]
+        return [ParamSpec(prefix + n["gate"] + self.suffix, (i, h)),
+                ParamSpec(prefix + n["up"] + self.suffix, (i, h)),
+                ParamSpec(prefix + n["down"] + self.suffix, (h, i))]
 
     def load(self, tensors, prefix):
         n = self.names
-        g, u = tensors.pop(prefix + n["gate"] + ".weight"), tensors.pop(prefix + n["up"] + ".weight")
+        g, u = tensors.pop(prefix + n["gate"] + self.suffix), tensors.pop(prefix + n["up"] + self.suffix)
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         del g, u
-        self.w_down = tensors.pop(prefix + n["down"] + ".weight").contiguous()
+        self.w_down = tensors.pop(prefix + n["down"] + self.suffix).contiguous()
 
     def forward(self, x, ctx):
         # few rows (decode): the activation is the epilogue of a weight-streaming product

@@ -1,5 +1,7 @@
-"""RMSNorm fused with the residual add that precedes it."""
+"""Norms fused with the residual add that precedes them."""
 from __future__ import annotations
+
+from typing import Optional
 
 import torch
 
@@ -32,4 +34,76 @@ class RMSNorm(Norm):
         return ops.add_rmsnorm(residual, delta, self.gain, out, self.eps, rows)
 
 
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b on x = residual + delta, all
+    in float32 (the variance from the deviations, in a second pass over the row).
+
+    ``residual`` is float32 [T, W], or [T, S, W] for S residual streams: the norm then reads
+    their sum.  ``delta`` is a tensor [T, W] (the plain residual add; one stream), or a
+    ``PendingUpdate`` of a block with several streams, folded in by the same launch.
+    Checkpoint tensors: ``prefix + weight_name`` and ``prefix + bias_name`` (None: no bias)."""
+
+    def __init__(self, size: int, eps: float, dtype, device, weight_name: str = "weight",
+                 bias_name: Optional[str] = "bias"):
+        self.size, self.eps, self.dtype, self.device = int(size), float(eps), dtype, device
+        self.weight_name, self.bias_name = weight_name, bias_name
+        self.gain = self.bias = None
+        self._ones = {}
+
+    def param_specs(self, prefix):
+        specs = [ParamSpec(prefix + self.weight_name, (self.size,))]
+        if self.bias_name is not None:
+            specs.append(ParamSpec(prefix + self.bias_name, (self.size,)))
+        return specs
+
+    def load(self, tensors, prefix):
+        self.gain = tensors[prefix + self.weight_name].to(torch.float32).contiguous()
+        if self.bias_name is not None:
+            self.bias = tensors[prefix + self.bias_name].to(torch.float32).contiguous()
+
+    def identity(self, streams: int, device):
+        """(mix, beta, alpha) of a plain residual add: the streams unchanged, the delta added to each."""
+        got = self._ones.get(streams)
+        if got is None:
+            got = self._ones[streams] = (torch.eye(streams, dtype=torch.float32, device=device).contiguous(),
+                                         torch.ones(streams, dtype=torch.float32, device=device))
+        return got
+
+    def norm_streams(self, streams, pending, alpha, rows=None, out_dtype=None):
+        """The norm of sum_j alpha_j r_j after ``pending`` (a ``PendingUpdate`` or None) is folded in."""
+        n = streams.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=out_dtype or self.dtype, device=streams.device)
+        eye, ones = self.identity(streams.shape[1], streams.device)
+        if pending is None:
+            y, mix, beta = None, eye, ones
+        else:
+            y, mix, beta = pending.y, pending.mix, pending.beta
+        return ops.stream_norm(streams, y, mix, beta, ones if alpha is None else alpha, self.gain, self.bias, out,
+                               self.eps, rows)
+
+    def as_pending(self, delta, streams):
+        """A plain delta (added to every stream) as a ``PendingUpdate``."""
+        eye, ones = self.identity(streams.shape[1], streams.device)
+        return PendingUpdate(delta, eye, ones)
+
+    def add_norm(self, residual, delta, rows=None, out_dtype=None):
+        streams = residual if residual.dim() == 3 else residual.view(residual.shape[0], 1, residual.shape[1])
+        if delta is not None and not isinstance(delta, PendingUpdate):
+            delta = self.as_pending(delta, streams)
+        return self.norm_streams(streams, delta, None, rows, out_dtype)
+
+    def kernel_libraries(self, dtype):
+        return [("streams", None)]
+
+
+class PendingUpdate:
+    """A sublayer's output that is not yet folded into the residual streams: r'_j = sum_s
+    mix[s, j] r_s + beta[j] y.  The next norm's launch does it."""
+    __slots__ = ("y", "mix", "beta")
+
+    def __init__(self, y, mix, beta):
+        self.y, self.mix, self.beta = y, mix, beta
+
+
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+register_part("norm", "layernorm", LayerNorm, replace=True)
