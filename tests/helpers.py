@@ -62,3 +62,87 @@ def load_plain(folder: str):
     return cfg, w
 
 
+
+
+# ---------------------------------------------------------------- Gebadra: tiny configurations
+def _lin(heads, dim, vdim, decay):
+    return dict(heads=heads, dim=dim, vdim=vdim, decay=list(decay))
+
+
+def _soft(heads, kv, dim, vdim, window, pool, rot_dims, base, factor, scale):
+    rot = dict(base=base, dims=rot_dims)
+    if factor is not None:
+        rot["scaling"] = dict(factor=factor)
+    return dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, mask=dict(size=window, pool=pool), rot=rot,
+                scale=scale)
+
+
+# three residual streams, one key/value head, a rotation on half of each head, a layer that runs
+# another's tensors (of each type), widths that differ between keys and values
+GEB_A = dict(
+    architecture="Gebadra", width=64, vocab=300, streams=3, norm=dict(eps=1e-5),
+    layers=[
+        dict(type="lightning", mixer=_lin(2, 16, 24, [0.9, 0.99]), mlp=dict(kind="dense", ff=96)),
+        dict(type="parallel", mixer=dict(left=_soft(4, 1, 32, 16, 20, 4, 16, 10000.0, 2.0, 0.2),
+                                         right=_lin(2, 16, 32, [0.8, 0.97])), mlp=dict(kind="dense", ff=80)),
+        dict(type="lightning", mixer=_lin(2, 16, 24, [0.9, 0.99]), mlp=dict(kind="dense", ff=96), weights_of=0),
+        dict(type="parallel", mixer=dict(left=_soft(4, 1, 32, 16, 20, 4, 16, 10000.0, 2.0, 0.2),
+                                         right=_lin(2, 16, 32, [0.8, 0.97])), mlp=dict(kind="dense", ff=80),
+             weights_of=1),
+    ])
+# the plain residual sum (no streams key), a window shorter than a block, as many key/value heads as
+# heads, no scaling of the rotation, a layer without feed-forward, one head
+GEB_B = dict(
+    architecture="Gebadra", width=96, vocab=211, norm=dict(eps=1e-6),
+    layers=[
+        dict(type="parallel", mixer=dict(left=_soft(3, 3, 24, 40, 7, 8, 24, 500.0, None, 0.3),
+                                         right=_lin(3, 40, 8, [0.5, 0.9, 0.999])), mlp=dict(kind="dense", ff=64)),
+        dict(type="lightning", mixer=_lin(1, 48, 64, [0.95]), mlp=None),
+    ])
+# one stream with its own connection tensors, blocks as long as a page, keys wider than 128 in the
+# recurrence, a window that is no multiple of anything
+GEB_C = dict(
+    architecture="Gebadra", width=128, vocab=257, streams=1, norm=dict(eps=1e-6),
+    layers=[
+        dict(type="lightning", mixer=_lin(2, 160, 16, [0.9, 0.98]), mlp=dict(kind="dense", ff=72)),
+        dict(type="parallel", mixer=dict(left=_soft(6, 2, 64, 64, 33, 16, 32, 100000.0, 4.0, 0.125),
+                                         right=_lin(4, 24, 40, [0.7, 0.9, 0.97, 0.995])),
+             mlp=dict(kind="dense", ff=72)),
+    ])
+GEBADRA = {"A": (GEB_A, 11, 8), "B": (GEB_B, 12, 8), "C": (GEB_C, 13, 16)}     # config, seed, page tokens
+
+
+def make_gebadra_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str:
+    """A model folder with seeded random weights through the engine's random-weights mode, then
+    reshaped so that no mechanism is a near-identity: projections large enough for sharp softmaxes
+    and gates away from one half, stream mixtures and head mixtures with off-diagonal weight."""
+    from paged_batch_engine_b200.config import load_config
+    from paged_batch_engine_b200.engine.runner import build_model
+    from paged_batch_engine_b200.weights import write_random_model
+    from safetensors.torch import load_file, save_file
+    _, typed = load_config(cfg)
+    model = build_model(typed, torch.float32, "cpu")
+    write_random_model(str(path), typed, model.param_specs(), seed, dtype)
+    f = os.path.join(str(path), "model.safetensors")
+    w = load_file(f)
+    g = torch.Generator().manual_seed(seed)
+    for k in list(w):
+        t = w[k].float()
+        leaf = k.split(".")[-1]
+        if k.endswith(".mix") and ".hc" in k:
+            t = torch.eye(t.shape[0]) * 0.8 + torch.randn(t.shape, generator=g) * 0.15
+        elif leaf in ("in", "out") and ".hc" in k:
+            t = 0.6 + 0.3 * torch.rand(t.shape, generator=g)
+        elif leaf == "talk":
+            t = torch.eye(t.shape[0]) * 0.7 + torch.randn(t.shape, generator=g) * 0.2
+        elif leaf in ("q", "k") and t.dim() == 2:
+            t = t * 6.0
+        elif leaf in ("v", "g", "o", "gate", "up", "down") and t.dim() == 2:
+            t = t * 1.5
+        elif leaf == "b":
+            t = torch.randn(t.shape, generator=g) * 0.1
+        elif k == "head":
+            t = t * 5.0
+        w[k] = t.to(w[k].dtype)
+    save_file(w, f)
+    return str(path)
