@@ -11,6 +11,14 @@
 // its column and takes its dot product with q_t.  The next token's q, k and v are fetched
 // while the current one is computed.  Prompt portions and single decoded tokens take the same
 // path: a request brings q_len rows.
+//
+// Long prompt portions are cut into chunks that run side by side (the launcher's work items):
+// first every chunk but a request's last runs from a zero state and leaves only its own
+// contribution U_c = sum_j lambda^(n_c-1-j) k_j v_j^T in scratch memory; a scan then turns these
+// into the states at the chunks' starts, S_c = lambda^(n_{c-1}) S_{c-1} + U_{c-1}, beginning with
+// the request's state row; last, every chunk runs again from its start state and writes its
+// outputs, the request's last chunk leaving the new state in the row.  The arithmetic per token
+// is the recurrence's own, so a cut changes a result by the rounding of float32 sums only.
 #include "common.cuh"
 #include "pdl.cuh"
 
@@ -28,6 +36,11 @@ struct LinAttnParams {
   const int32_t* q_start;   // [R]
   const int32_t* q_len;     // [R]
   const int32_t* slots;     // [R] state row of each request
+  // work items instead of requests when not null: [n, 4] = first batch row, rows, where the state
+  // comes from, where it goes; a place is a row of `state` (v >= 0), nothing / zeros (-1), or
+  // entry -(v + 2) of `scratch` (v <= -2)
+  const int32_t* items;
+  float* scratch;           // [entries, H, D, E]
   int H, D, E;
   float k_scale;
   int act;                  // 1: silu on q, k and v
@@ -48,15 +61,28 @@ __global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
   const int part = lane % PARTS, col = lane / PARTS;
   const int e = blockIdx.z * COLS + col;
   const int D = p.D, E = p.E, H = p.H;
-  const int n = p.q_len[r];
+  int n, t0, src, dst;
+  if (p.items) {
+    const int32_t* it = p.items + (size_t)r * 4;
+    t0 = it[0]; n = it[1]; src = it[2]; dst = it[3];
+  } else {
+    n = p.q_len[r];
+    t0 = p.q_start[r];
+    src = dst = n > 0 ? p.slots[r] : -1;
+  }
   if (n <= 0) return;
-  const int t0 = p.q_start[r];
   const bool live = e < E;
   const int d0 = part * DPT;                   // this lane's first state row
-  float* st = p.state + (((size_t)p.slots[r] * H + h) * D) * E;
+  const size_t per_head = (size_t)D * E;
+  auto place = [&](int v) -> float* {
+    if (v == -1) return nullptr;
+    return (v >= 0 ? p.state + (size_t)v * H * per_head : p.scratch + (size_t)(-(v + 2)) * H * per_head) + h * per_head;
+  };
+  const float* st_in = place(src);
+  float* st = place(dst);
   float S[DPT];
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) S[i] = (live && d0 + i < D) ? st[(size_t)(d0 + i) * E + e] : 0.f;
+  for (int i = 0; i < DPT; ++i) S[i] = (st_in && live && d0 + i < D) ? st_in[(size_t)(d0 + i) * E + e] : 0.f;
   const float lam = p.decay[h];
   const T* qp = (const T*)p.q + (size_t)h * D;
   const T* kp = (const T*)p.k + (size_t)h * D;
@@ -103,12 +129,41 @@ __global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
     }
 #pragma unroll
     for (int m = 1; m < PARTS; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-    if (live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = o;
+    if (p.out && live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = o;
   }
-  if (live) {
+  if (live && st) {
 #pragma unroll
     for (int i = 0; i < DPT; ++i)
       if (d0 + i < D) st[(size_t)(d0 + i) * E + e] = S[i];
+  }
+}
+
+// The states at the chunks' starts from the chunks' own contributions, in place (see the top).
+struct ScanParams {
+  float* state;
+  float* scratch;
+  const float* decay;
+  const int32_t* desc;      // [m, 4]: state row, first scratch entry, chunks, rows of every chunk but the last
+  int H, D, E;
+};
+
+__global__ void chunk_scan_kernel(ScanParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int32_t* d = p.desc + (size_t)blockIdx.x * 4;
+  const int h = blockIdx.y;
+  const size_t per_head = (size_t)p.D * p.E;
+  const size_t i = (size_t)blockIdx.z * blockDim.x + threadIdx.x;
+  if (i >= per_head) return;
+  const float lam = p.decay[h];
+  float lam_n = 1.f;
+  for (int j = 0; j < d[3]; ++j) lam_n *= lam;
+  float S = p.state[((size_t)d[0] * p.H + h) * per_head + i];
+  for (int c = 0; c < d[2]; ++c) {
+    float* u = p.scratch + ((size_t)(d[1] + c) * p.H + h) * per_head + i;
+    const float own = c + 1 < d[2] ? *u : 0.f;
+    *u = S;
+    S = fmaf(lam_n, S, own);
   }
 }
 
@@ -135,9 +190,18 @@ int dispatch_la(const LinAttnParams& p, int R, cudaStream_t stream) {
 
 PBE_EXPORT int pbe_linear_attention(const void* q, const void* k, const void* v, int ld, int dtype, float* out,
                                     float* state, const float* decay, const int32_t* q_start, const int32_t* q_len,
-                                    const int32_t* slots, int R, int H, int D, int E, float k_scale, int act,
-                                    cudaStream_t stream) {
+                                    const int32_t* slots, const int32_t* items, float* scratch, int R, int H, int D,
+                                    int E, float k_scale, int act, cudaStream_t stream) {
   if (R <= 0) return 0;
-  LinAttnParams p{q, k, v, ld, out, state, decay, q_start, q_len, slots, H, D, E, k_scale, act};
+  LinAttnParams p{q, k, v, ld, out, state, decay, q_start, q_len, slots, items, scratch, H, D, E, k_scale, act};
   return dtype == PBE_F32 ? dispatch_la<float>(p, R, stream) : dispatch_la<__nv_bfloat16>(p, R, stream);
+}
+
+PBE_EXPORT int pbe_linear_attention_scan(float* state, float* scratch, const float* decay, const int32_t* desc,
+                                         int m, int H, int D, int E, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  ScanParams p{state, scratch, decay, desc, H, D, E};
+  dim3 grid(m, H, (unsigned)(((size_t)D * E + 255) / 256));
+  launch_k(chunk_scan_kernel, grid, 256, 0, stream, p);
+  return launch_status();
 }

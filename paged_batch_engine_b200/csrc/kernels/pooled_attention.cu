@@ -70,8 +70,10 @@ __global__ void qk_prepare_kernel(QkPrepParams p) {
     k_scale = rsqrtf(block_sum(ss, red) / (float)(G * D) + p.eps);
   }
   const float pos = (float)p.positions[t];
-  const int slot = p.slots ? p.slots[t] : 0;
-  const int page = slot / PT, off = slot - page * PT;
+  // a negative slot (the padding rows of a captured step): nothing is written
+  const int slot = p.slots ? p.slots[t] : -1;
+  const bool store = slot >= 0;
+  const int page = store ? slot / PT : 0, off = store ? slot - page * PT : 0;
   const int half = D / 2;       // pairs per head (D is even)
   T* qo = (T*)p.q_out + (size_t)t * H * D;
   // pairs of the query heads, then of the key heads
@@ -98,13 +100,13 @@ __global__ void qk_prepare_kernel(QkPrepParams p) {
     if (is_q) {
       qo[e0] = from_float<T>(a);
       qo[e0 + 1] = from_float<T>(b);
-    } else if (p.k_pages) {
+    } else if (p.k_pages && store) {
       T* dst = (T*)p.k_pages + (((size_t)page * G + head) * PT + off) * D + 2 * pr;
       dst[0] = from_float<T>(a);
       dst[1] = from_float<T>(b);
     }
   }
-  if (p.v_pages) {
+  if (p.v_pages && store) {
     for (int i = threadIdx.x; i < G * E; i += blockDim.x) {
       const int head = i / E, e = i - head * E;
       ((T*)p.v_pages)[(((size_t)page * G + head) * PT + off) * E + e] = v[i];

@@ -240,11 +240,13 @@ def _column_slice(x: torch.Tensor, what: str):
 
 def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
                      q_start: torch.Tensor, q_len: torch.Tensor, slots: torch.Tensor, num_requests: int,
-                     heads: int, k_scale: float = 1.0, silu: bool = False) -> torch.Tensor:
+                     heads: int, k_scale: float = 1.0, silu: bool = False, plan=None) -> torch.Tensor:
     """o_t = S_t^T q_t with S_t = decay_h S_{t-1} + k_t v_t^T per head, request by request over
     the rows each brings (``q_start``, ``q_len`` int32 [R]); ``state`` float32 [slots, H, D, E]
     is read at ``slots[r]`` and left updated.  q, k [T, H*D] and v [T, H*E] are column slices of
-    one projection matrix (equal row stride).  Returns float32 [T, H*E]."""
+    one projection matrix (equal row stride).  ``plan`` (a ``RecurrencePlan`` of the step): long
+    portions are cut into chunks that run side by side, their start states made by a scan over
+    the chunks' own contributions.  Returns float32 [T, H*E]."""
     _need_cuda(q, k, v, state, decay, q_start, q_len, slots)
     for x in (q, k, v):
         _column_slice(x, "linear_attention")
@@ -268,11 +270,23 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: t
         raise KernelError(f"linear_attention: key width {D} per head is beyond 512")
     out = torch.empty((T, heads * E), dtype=torch.float32, device=q.device)
     fn = _fn("linear_attention", "pbe_linear_attention",
-             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
-    _check(fn(_ptr(q), _ptr(k), _ptr(v), ld, _dtype_code(q), _ptr(out), _ptr(state), _ptr(decay), _ptr(q_start),
-              _ptr(q_len), _ptr(slots), num_requests, heads, D, E, float(k_scale), 1 if silu else 0, _stream()),
-           "linear_attention")
+             [c_void_p, c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int,
+                                                                             c_void_p])
+
+    def launch(result, items, scratch, n):
+        _check(fn(_ptr(q), _ptr(k), _ptr(v), ld, _dtype_code(q), _ptr(result), _ptr(state), _ptr(decay), _ptr(q_start),
+                  _ptr(q_len), _ptr(slots), _ptr(items), _ptr(scratch), n, heads, D, E, float(k_scale),
+                  1 if silu else 0, _stream()), "linear_attention")
+    if plan is None or plan.num_chunks == 0:
+        launch(out, None, None, num_requests)
+        return out
+    scratch = torch.empty((plan.num_chunks, heads, D, E), dtype=torch.float32, device=q.device)
+    launch(None, plan.first_pass, scratch, plan.num_first_pass)          # the chunks' own contributions
+    scan = _fn("linear_attention", "pbe_linear_attention_scan",
+               [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(scan(_ptr(state), _ptr(scratch), _ptr(decay), _ptr(plan.scan), plan.num_scan, heads, D, E, _stream()),
+           "linear_attention_scan")
+    launch(out, plan.second_pass, scratch, plan.num_second_pass)         # every chunk from its start state
     return out
 
 

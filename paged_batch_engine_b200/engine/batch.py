@@ -215,6 +215,44 @@ class _Packer:
         return self.device_buffer[o:o + n].view(shape)
 
 
+RECURRENCE_CHUNK = 64       # rows of a chunk when a long portion's recurrence is cut to run side by side
+
+
+@dataclass
+class RecurrencePlan:
+    """How the rows of a step are cut for a recurrent mixer (see ``StepContext.recurrence_plan``).
+    A place is a state row (v >= 0), nothing (-1) or scratch entry -(v + 2)."""
+    num_chunks: int                 # scratch entries (0: no request is cut, the plan is not needed)
+    first_pass: Optional[torch.Tensor] = None     # int32 [n, 4]: first row, rows, state from, state to
+    num_first_pass: int = 0
+    scan: Optional[torch.Tensor] = None           # int32 [m, 4]: state row, first scratch entry, chunks, rows a chunk
+    num_scan: int = 0
+    second_pass: Optional[torch.Tensor] = None
+    num_second_pass: int = 0
+
+
+def recurrence_plan_arrays(q_start, q_len, slots, chunk: int):
+    """Host arrays of a ``RecurrencePlan``: requests of at least two chunks are cut into chunks of
+    ``chunk`` rows (the last takes the rest); every other request is one item from and to its
+    state row.  Returns (first_pass, scan, second_pass, scratch entries)."""
+    first, scan, second, entries = [], [], [], 0
+    for qs, n, slot in zip(q_start, q_len, slots):
+        qs, n, slot = int(qs), int(n), int(slot)
+        if n < 2 * chunk:
+            second.append((qs, n, slot, slot))
+            continue
+        chunks = (n + chunk - 1) // chunk
+        scan.append((slot, entries, chunks, chunk))
+        for c in range(chunks):
+            rows = min(chunk, n - c * chunk)
+            place = -(entries + c + 2)
+            if c + 1 < chunks:
+                first.append((qs + c * chunk, rows, -1, place))
+            second.append((qs + c * chunk, rows, place, slot if c + 1 == chunks else -1))
+        entries += chunks
+    return first, scan, second, entries
+
+
 class StepContext:
     """Everything the parts read about the step besides their input rows."""
     captured = False              # True for the fixed-layout context of a captured decode step
@@ -328,6 +366,26 @@ class StepContext:
 
     def group(self, g: int) -> GroupArrays:
         return self._groups[g]
+
+    def recurrence_plan(self, chunk: int = RECURRENCE_CHUNK) -> RecurrencePlan:
+        """The step's rows cut for a recurrence over each request's rows (made on first use, one
+        copy to the device for all layers of the step)."""
+        plan = getattr(self, "_recurrence_plan", None)
+        if plan is None:
+            first, scan, second, entries = recurrence_plan_arrays(self.q_start_host, self.q_len_host,
+                                                                  self.state_slots_host, chunk)
+            if entries == 0:
+                plan = RecurrencePlan(0)
+            else:
+                host = torch.tensor(first + scan + second, dtype=torch.int32)
+                if torch.cuda.is_available():
+                    host = host.pin_memory()
+                dev = host.to(self.device, non_blocking=True)
+                a, b = len(first), len(first) + len(scan)
+                plan = RecurrencePlan(entries, dev[:a], a, dev[a:b], len(scan), dev[b:], len(second))
+                self._plan_host = host
+            self._recurrence_plan = plan
+        return plan
 
     def row_tiles(self, tile_rows: int):
         """(int32 [n, 3] on the device, n): the step's rows cut into tiles of at most ``tile_rows``

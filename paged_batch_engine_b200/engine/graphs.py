@@ -77,8 +77,9 @@ class DecodeStepContext(StepContext):
             n = int(np.prod(shape))
             lay[name] = (off, tuple(shape))
             off += (n + 3) // 4 * 4
-        for name in ("tokens", "positions", "q_start", "q_len", "seq_len", "want", "state"):
+        for name in ("tokens", "positions", "q_start", "q_len", "seq_len", "want", "state", "row_request"):
             place(name, (B,))
+        place("row_tiles", (B, 3))
         for g, stride in enumerate(bt_strides):
             place(f"bt{g}", (B, stride))
             place(f"slots{g}", (B,))
@@ -116,6 +117,11 @@ class DecodeStepContext(StepContext):
                         for g, stride in enumerate(bt_strides)]
         self._h("q_start")[:] = np.arange(B)
         self._h("want")[:] = np.arange(B)
+        # row i is request i's only row: the row's request, and the rows as tiles of one row each
+        self.request_of_row = view("row_request")
+        self._h("row_request")[:] = np.arange(B)
+        self._tiles = view("row_tiles")
+        self._h("row_tiles")[:] = np.stack([np.arange(B), np.arange(B), np.ones(B, dtype=np.int64)], axis=1)
         for i, _ in enumerate(self.work_keys):
             self._h(f"tsr{i}")[:] = np.arange(B)
             self._h(f"st{i}")[:] = np.arange(B)
@@ -188,6 +194,11 @@ class DecodeStepContext(StepContext):
         if self._copied is not None:
             self._copied.record()
             self._copy_pending = True
+
+    def row_tiles(self, tile_rows: int):
+        """Every row is a tile of its own, whatever tile size is asked for (rows beyond the live
+        requests see no keys: their block tables hold no page)."""
+        return self._tiles, self.batch
 
     def attention_work(self, group, group_size, tile_rows, window, num_heads, head_dim):
         w = self._work[(group, group_size, tile_rows, window)]

@@ -76,8 +76,10 @@ class DecayLinearAttention(Mixer):
         proj = ops.linear(x, self.w_in, None, out_dtype=self.dtype, kind=1)
         q, k = proj[:, :H * D], proj[:, H * D:2 * H * D]
         v, g = proj[:, 2 * H * D:2 * H * D + H * E], proj[:, 2 * H * D + H * E:]
+        # long portions run as chunks side by side; a captured step (single tokens) has no plan
+        plan = None if getattr(ctx, "captured", False) else ctx.recurrence_plan()
         o = ops.linear_attention(q, k, v, cache.state, self.decay, ctx.q_start, ctx.q_len, ctx.state_slots,
-                                 ctx.num_requests, H, self.key_scale, self.activation == "silu")
+                                 ctx.num_requests, H, self.key_scale, self.activation == "silu", plan)
         y = ops.gated_rms(o, g, self.gain, H, self.eps, self.out_norm == "head", self.gate, self.dtype)
         return ops.linear(y, self.w_o, None, out_dtype=self.dtype, kind=2)
 

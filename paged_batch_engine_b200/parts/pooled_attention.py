@@ -30,7 +30,7 @@ class PooledWindowAttention(Mixer):
     hidden], v [G*E, hidden], o [hidden, H*E], q.norm [H*D], k.norm [G*D], talk [H, H]."""
     TENSOR_NAMES = dict(q="q_proj", k="k_proj", v="v_proj", o="o_proj", q_norm="q_norm", k_norm="k_norm",
                         talk="talk")
-    decode_capturable = False     # the row tiles of a step are made on the host
+    decode_capturable = True      # decoded tokens are stepped from the step's device arrays alone
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
                  scale: float, window: int, eps: float, dtype, device, pool: Optional[int] = None,
@@ -124,7 +124,8 @@ class PooledWindowAttention(Mixer):
                                 bt_pool, self.pool, ctx.page_tokens)
         if self._tile_rows is None:
             self._tile_rows = ops.pooled_attention_tile_rows(H, E, 16)
-        single = int(ctx.q_len_host.max(initial=1)) == 1      # decoded tokens only: a row a tile
+        # decoded tokens only (always so in a captured step): a row a tile
+        single = getattr(ctx, "captured", False) or int(ctx.q_len_host.max(initial=1)) == 1
         rows = 1 if single else self._tile_rows
         tiles, n_tiles = ctx.row_tiles(rows)
         out = ops.pooled_attention(q, tok.k, tok.v, k_pool, v_pool, self.talk, tiles, n_tiles, rows, ctx.q_start,
