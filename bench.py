@@ -218,6 +218,10 @@ def main():
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--design", default=None, choices=["gebadra"],
+                    help="instead of the default workload: prefill and decode of a few layers of this design at "
+                         "real layer sizes beside the Qwen2 model of equal sizes, with per-kernel rooflines")
+    ap.add_argument("--sizes", default="2048,4096", help="model widths of the --design comparison")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-extended", action="store_true",
                     help="skip the points at 8,192-token contexts, the float32 path and the scheduler workloads")
@@ -233,6 +237,11 @@ def main():
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.design:
+        import bench_design
+        print(json.dumps(bench_design.run(args.design, min(steps, 32), warmup,
+                                          tuple(int(x) for x in args.sizes.split(",")))))
+        return 0
 
     import torch
     from paged_batch_engine_b200 import Engine

@@ -1,0 +1,246 @@
+#!/usr/bin/env python3
+"""A design beside the engine's closest existing model at equal layer sizes (random weights).
+
+    python bench.py --design gebadra [--steps K] [--warmup W] [--sizes 2048,4096]
+
+For each size: prefill (one 2,048-token prompt in one step) and decode (batch 8 from 2,048-token
+contexts, the captured decode step) throughput of a few layers of the design and of a Qwen2 model
+with the same width, heads, key/value heads, feed-forward width, vocabulary and number of
+layers; and the device time of the design's own kernels in one prompt step and one decode step,
+each beside the like kernel of the Qwen2 model, with the fraction of its roofline (the slower of
+algorithmic bytes over the measured copy bandwidth and algorithmic FLOPs over the measured bf16
+GEMM rate).  Times are CUDA events on the launching stream after warm-up; the per-kernel times
+bracket every launch of that kernel in an eager step.  Prints ONE JSON line.
+"""
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT = 2048
+BATCH = 8
+LAYERS = 4
+
+
+def gebadra_config(width: int) -> dict:
+    heads, kv, dim, ff = width // 128, max(1, width // 512), 128, {2048: 5632, 4096: 11008}.get(width, width * 11 // 4)
+    decay = [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads - 1)) for h in range(heads)]
+    lin = dict(heads=heads, dim=dim, vdim=dim, decay=decay)
+    par = dict(left=dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, mask=dict(size=1024, pool=64),
+                         rot=dict(base=500000.0, dims=64, scaling=dict(factor=8.0)), scale=dim ** -0.5),
+               right=dict(heads=heads, dim=dim // 2, vdim=dim, decay=decay))
+    mlp = dict(kind="dense", ff=ff)
+    kinds = ["lightning", "parallel", "lightning", "lightning"][:LAYERS]
+    layers = [dict(type=k, mixer=lin if k == "lightning" else par, mlp=mlp) for k in kinds]
+    return dict(architecture="Gebadra", width=width, vocab=32000, streams=2, norm=dict(eps=1e-6), layers=layers)
+
+
+def qwen_config(width: int) -> dict:
+    g = gebadra_config(width)
+    heads = g["layers"][0]["mixer"]["heads"]
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=width, num_hidden_layers=LAYERS,
+                num_attention_heads=heads, num_key_value_heads=g["layers"][1]["mixer"]["left"]["kv_heads"], head_dim=128,
+                intermediate_size=g["layers"][0]["mlp"]["ff"], vocab_size=32000, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False, hidden_act="silu",
+                eos_token_id=31999)
+
+
+class OpTimer:
+    """Brackets every call of the named functions of ``ops`` with CUDA events."""
+
+    def __init__(self, names):
+        from paged_batch_engine_b200.csrc import ops
+        self.ops, self.names, self.saved, self.events = ops, names, {}, []
+        self.spin = 800000          # cycles (about 0.4 ms) the device spins before every bracket
+
+    def __enter__(self):
+        import torch
+        for n in self.names:
+            fn = getattr(self.ops, n)
+            self.saved[n] = fn
+
+            def timed(*a, _fn=fn, _n=n, **kw):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                # the device idles ahead of the bracket while the host enqueues what is inside it, so
+                # that the bracket holds device time and not the interpreter's
+                torch.cuda._sleep(self.spin)
+                s.record()
+                out = _fn(*a, **kw)
+                e.record()
+                self.events.append((_n, s, e))
+                return out
+            setattr(self.ops, n, timed)
+        return self
+
+    def __exit__(self, *exc):
+        for n, fn in self.saved.items():
+            setattr(self.ops, n, fn)
+
+    def totals(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for n, s, e in self.events:
+            ms, calls = out.get(n, (0.0, 0))
+            out[n] = (ms + s.elapsed_time(e), calls + 1)
+        return out
+
+
+def _prefill(runner, tokens, want_ops=None):
+    import torch
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    cache = runner.cache
+    g = torch.Generator().manual_seed(5)
+    vocab = runner.model.spec.vocab_size
+    times, per_op = [], None
+    for i in range(5):
+        prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+        h = cache.add_request()
+        assert cache.reserve(h, tokens)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        if want_ops and i == 4:
+            with OpTimer(want_ops) as t:
+                runner.step([StepEntry(h, prompt, [tokens - 1])])
+                per_op = t.totals()
+        else:
+            start.record()
+            runner.step([StepEntry(h, prompt, [tokens - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                times.append(start.elapsed_time(stop))
+        cache.free(h)
+    times.sort()
+    return times[len(times) // 2], per_op
+
+
+def _decode(runner, batch, context, steps, warmup, want_ops=None):
+    import torch
+    from paged_batch_engine_b200.csrc import ops
+    from paged_batch_engine_b200.engine.batch import StepEntry
+    cache = runner.cache
+    g = torch.Generator().manual_seed(6)
+    vocab = runner.model.spec.vocab_size
+    handles = []
+    for _ in range(batch):
+        h = cache.add_request()
+        assert cache.reserve(h, context)
+        runner.step([StepEntry(h, torch.randint(0, vocab, (context,), generator=g).tolist(), [])])
+        handles.append(h)
+    feed = torch.randint(0, vocab, (steps + warmup + 1, batch), generator=g).tolist()
+    out_ids = torch.empty(batch, dtype=torch.int32, device=runner.device)
+
+    def one(i, graph=True):
+        entries = [StepEntry(h, [feed[i][j]], [0]) for j, h in enumerate(handles)]
+        for e in entries:
+            assert cache.reserve(e.handle, 1)
+        ops.argmax(runner.step(entries, decode_graph=graph), out_ids)
+    for i in range(warmup):
+        one(i)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    per_op = None
+    if want_ops:
+        with OpTimer(want_ops) as t:
+            one(warmup + steps, graph=False)
+            per_op = t.totals()
+    captured = runner.graphs is not None and runner.graphs.replays > 0
+    for h in handles:
+        cache.free(h)
+    return ms, per_op, captured
+
+
+def rooflines(width: int, pk: dict):
+    """Algorithmic bytes and FLOPs of the compared kernels for the two workloads, per launch."""
+    g = gebadra_config(width)
+    lin, left = g["layers"][0]["mixer"], g["layers"][1]["mixer"]["left"]
+    H, D, E = lin["heads"], lin["dim"], lin["vdim"]
+    G, W, P = left["kv_heads"], left["mask"]["size"], left["mask"]["pool"]
+    T, R, C = PROMPT, BATCH, PROMPT
+    keys_prefill = sum(min(t + 1, W) + max(0, (t - W + 1) // P) for t in range(T))
+    keys_decode = min(C + 1, W) + max(0, (C - W + 1) // P)
+
+    def t_us(b, f):
+        return max(b / (pk["hbm_gbs"] * 1e9), f / (pk["bf16_tflops"] * 1e12)) * 1e6
+    return {
+        "prefill": {
+            "linear_attention": t_us(2 * T * H * (2 * D + E) + 4 * T * H * E + 8 * H * D * E, 4 * T * H * D * E),
+            "pooled_attention": t_us(2 * (T * H * (D + E) + T * G * (D + E) * (1 + 1 / P)), 2 * H * (D + E) * keys_prefill),
+            "stream_norm": t_us(T * width * (2 * 4 * 2 + 2 + 2), 0),
+            "paged_attention": t_us(2 * (2 * T * H * 128 + 2 * T * G * 128), 4 * H * 128 * T * (T + 1) / 2),
+            "add_rmsnorm": t_us(T * width * (2 * 4 + 2 + 2), 0),
+        },
+        "decode": {
+            "linear_attention": t_us(2 * R * H * (2 * D + E) + 4 * R * H * E + 8 * R * H * D * E, 4 * R * H * D * E),
+            "pooled_attention": t_us(2 * R * keys_decode * G * (D + E), 2 * R * H * (D + E) * keys_decode),
+            "stream_norm": t_us(R * width * (2 * 4 * 2 + 2 + 2), 0),
+            "attention_decode_fused": t_us(2 * R * C * G * 2 * 128, 4 * R * H * 128 * C),
+            "paged_attention": t_us(2 * R * C * G * 2 * 128, 4 * R * H * 128 * C),
+            "add_rmsnorm": t_us(R * width * (2 * 4 + 2 + 2), 0),
+        },
+    }
+
+
+def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
+    import gc
+    import torch
+    from bench import ClockSampler, peaks
+    from paged_batch_engine_b200.config import load_config
+    from paged_batch_engine_b200.engine.runner import ModelRunner
+    if design != "gebadra":
+        raise SystemExit(f"unknown design {design!r}; known: gebadra")
+    os.environ["PBE_EXEC"] = "python"        # per-kernel times need every launch to come through ops
+    pk = peaks()
+    page = 16
+    pool = BATCH * (PROMPT + steps + warmup + 64) + PROMPT + 64
+    own = ["linear_attention", "pooled_attention", "stream_norm", "gated_rms", "qk_prepare", "pool_blocks",
+           "branch_rms_mean"]
+    theirs = ["paged_attention", "attention_decode_fused", "add_rmsnorm", "rope_kv_write"]
+    sampler = ClockSampler(0)
+    sampler.active = True
+    out = {}
+    for width in sizes:
+        roof = rooflines(width, pk)
+        row = {}
+        for name, cfg, names in (("gebadra", gebadra_config(width), own), ("qwen2", qwen_config(width), theirs)):
+            _, typed = load_config(cfg)
+            runner = ModelRunner.from_random(typed, seed=0, dtype="bfloat16", page_tokens=page, max_cache_tokens=pool,
+                                             max_requests=BATCH + 1)
+            ms_p, ops_p = _prefill(runner, PROMPT, names)
+            ms_d, ops_d, captured = _decode(runner, BATCH, PROMPT, steps, warmup, names)
+            kernels = {}
+            for phase, per_op in (("prefill", ops_p), ("decode", ops_d)):
+                for op, (ms, calls) in sorted((per_op or {}).items()):
+                    us = ms * 1e3 / calls
+                    entry = {"us": round(us, 1), "calls": calls}
+                    if op in roof[phase]:
+                        entry["roofline_us"] = round(roof[phase][op], 2)
+                        entry["frac"] = round(roof[phase][op] / us, 4)
+                    kernels[f"{phase}.{op}"] = entry
+            row[name] = {"prefill_tok_s": round(PROMPT * 1e3 / ms_p, 1), "prefill_ms": round(ms_p, 3),
+                         "decode_tok_s": round(BATCH * 1e3 / ms_d, 1), "decode_ms_per_step": round(ms_d, 4),
+                         "decode_captured": bool(captured), "kernels": kernels}
+            del runner
+            gc.collect()
+            torch.cuda.empty_cache()
+        out[str(width)] = row
+    sampler.active = False
+    return {"design": design, "beside": "qwen2 at equal width, heads, key/value heads, feed-forward, vocabulary, layers",
+            "layers": LAYERS, "prompt_tokens": PROMPT, "decode_batch": BATCH, "decode_context": PROMPT,
+            "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic (random weights)",
+            "peaks": {"source": pk["source"], "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
+            "sizes": out, "clocks": sampler.summary()}
+
+
+if __name__ == "__main__":
+    print(json.dumps(run("gebadra", 32, 5)))

@@ -113,20 +113,32 @@ __global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
     const float v = vn;
     __syncwarp();
     if (t + 1 < n) fetch(t + 1);
-    float o = 0.f;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;       // four chains: the sum's latency does not bind
+    if (p.out) {
 #pragma unroll
-    for (int i = 0; i < DPT; i += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(ks + d0 + i);
-      const float4 q4 = *reinterpret_cast<const float4*>(qs + d0 + i);
-      S[i] = fmaf(lam, S[i], k4.x * v);
-      o = fmaf(S[i], q4.x, o);
-      S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
-      o = fmaf(S[i + 1], q4.y, o);
-      S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
-      o = fmaf(S[i + 2], q4.z, o);
-      S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
-      o = fmaf(S[i + 3], q4.w, o);
+      for (int i = 0; i < DPT; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + d0 + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + d0 + i);
+        S[i] = fmaf(lam, S[i], k4.x * v);
+        o0 = fmaf(S[i], q4.x, o0);
+        S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
+        o1 = fmaf(S[i + 1], q4.y, o1);
+        S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
+        o2 = fmaf(S[i + 2], q4.z, o2);
+        S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
+        o3 = fmaf(S[i + 3], q4.w, o3);
+      }
+    } else {                                             // a chunk's own contribution only
+#pragma unroll
+      for (int i = 0; i < DPT; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + d0 + i);
+        S[i] = fmaf(lam, S[i], k4.x * v);
+        S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
+        S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
+        S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
+      }
     }
+    float o = (o0 + o1) + (o2 + o3);
 #pragma unroll
     for (int m = 1; m < PARTS; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
     if (p.out && live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = o;

@@ -181,6 +181,65 @@ struct PoolAttnParams {
 constexpr int PA_THREADS = 256;
 constexpr int PA_ACC = 32;      // outputs a thread accumulates at most
 
+__device__ __forceinline__ void unpack16(const uint4& r, float* f, float) {
+  f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& r, float* f, __nv_bfloat16) {
+  const unsigned w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// A tile of BN keys (or values), all G key/value heads of each, from the pages into shared memory
+// as float32 rows of `stride` floats: row j = [head 0's `width` elements, head 1's, ...]; keys that
+// do not exist (base < 0) become zeros.  Rows whose width fills 16-byte pieces travel as such,
+// four pieces a thread in flight.
+template <typename T>
+__device__ __forceinline__ void load_tile(float* dst, int stride, const T* src, const long long* base, int BN, int G,
+                                          int width, int PT) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  if (width % VEC == 0) {
+    const int wv = width / VEC, per_key = G * wv, total = BN * per_key;
+    constexpr int U = 4;
+    for (int i0 = threadIdx.x; i0 < total; i0 += PA_THREADS * U) {
+      uint4 r[U];
+      int at[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * PA_THREADS;
+        at[u] = -1;
+        r[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < total) {
+          const int j = i / per_key, c = i - j * per_key;
+          const int g = c / wv, dv = c - g * wv;
+          at[u] = j * stride + g * width + dv * VEC;
+          const long long b = base[j];
+          if (b >= 0) r[u] = *reinterpret_cast<const uint4*>(src + (b + (long long)g * PT) * width + dv * VEC);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (at[u] >= 0) {
+          float f[VEC];
+          unpack16(r[u], f, T());
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) dst[at[u] + x] = f[x];
+        }
+      }
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < BN * G * width; i += PA_THREADS) {
+    const int j = i / (G * width), c = i - j * (G * width);
+    const int g = c / width, d = c - g * width;
+    const long long b = base[j];
+    dst[j * stride + c] = b >= 0 ? to_float(src[(b + (long long)g * PT) * width + d]) : 0.f;
+  }
+}
+
 template <typename T, int BM>
 __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnParams p) {
   extern __shared__ __align__(16) float smem[];
@@ -244,21 +303,8 @@ __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnPa
       }
       __syncthreads();
       const T* kc = (const T*)(pooled ? p.k_pool : p.k_tok);
-      for (int i = threadIdx.x; i < BN * G * D; i += blockDim.x) {
-        const int j = i / (G * D), c = i - j * (G * D);
-        const int g = c / D, d = c - g * D;
-        const long long b = base[j];
-        Ks[j * KS + c] = b >= 0 ? to_float(kc[(b + (long long)g * PT) * D + d]) : 0.f;
-      }
-      if (pass == 1) {
-        const T* vc = (const T*)(pooled ? p.v_pool : p.v_tok);
-        for (int i = threadIdx.x; i < BN * G * E; i += blockDim.x) {
-          const int j = i / (G * E), c = i - j * (G * E);
-          const int g = c / E, e = c - g * E;
-          const long long b = base[j];
-          Vs[i] = b >= 0 ? to_float(vc[(b + (long long)g * PT) * E + e]) : 0.f;
-        }
-      }
+      load_tile<T>(Ks, KS, kc, base, BN, G, D, PT);
+      if (pass == 1) load_tile<T>(Vs, G * E, (const T*)(pooled ? p.v_pool : p.v_tok), base, BN, G, E, PT);
       __syncthreads();
       // scores of every (row, head) against the tile's keys; -inf where the row does not see the key
       for (int i = threadIdx.x; i < BM * H * BN; i += blockDim.x) {
@@ -274,23 +320,35 @@ __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnPa
           const float* qr = Qs + (size_t)row * H * D + h * D;
           const float* kr = Ks + j * KS + (h / rep) * D;
           float a = 0.f;
-          for (int d = 0; d < D; ++d) a = fmaf(qr[d], kr[d], a);
+          if ((D & 3) == 0) {
+            for (int d = 0; d < D; d += 4) {
+              const float4 q4 = *reinterpret_cast<const float4*>(qr + d);
+              a = fmaf(q4.x, kr[d], a);
+              a = fmaf(q4.y, kr[d + 1], a);
+              a = fmaf(q4.z, kr[d + 2], a);
+              a = fmaf(q4.w, kr[d + 3], a);
+            }
+          } else {
+            for (int d = 0; d < D; ++d) a = fmaf(qr[d], kr[d], a);
+          }
           s = a;
         }
         Ss[i] = s;
       }
       __syncthreads();
       if (pass == 0) {
-        for (int rh = threadIdx.x; rh < BM * H; rh += blockDim.x) {
-          const float* s = Ss + (size_t)rh * BN;
-          float m = Ms[rh];
-          float mx = m;
-          for (int j = 0; j < BN; ++j) mx = fmaxf(mx, s[j]);
-          if (mx == -INFINITY) continue;
-          float l = Ls[rh] * expf(m - mx);
-          for (int j = 0; j < BN; ++j) l += expf(s[j] - mx);
-          Ms[rh] = mx;
-          Ls[rh] = l;
+        // a warp per (row, head), a key per lane (BN <= 32)
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int rh = warp; rh < BM * H; rh += PA_THREADS / 32) {
+          const float sc = lane < BN ? Ss[(size_t)rh * BN + lane] : -INFINITY;
+          const float m = Ms[rh];
+          const float mx = fmaxf(m, warp_max(sc));
+          if (mx == -INFINITY) continue;          // the same for the whole warp
+          const float sum = warp_sum(expf(sc - mx));
+          if (lane == 0) {
+            Ls[rh] = Ls[rh] * expf(m - mx) + sum;
+            Ms[rh] = mx;
+          }
         }
         continue;
       }
@@ -322,7 +380,14 @@ __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnPa
           const float* w = Wp + (size_t)rh * BN;
           const float* vcol = Vs + (h / rep) * E + e;
           float a = acc[u];
-          for (int j = 0; j < BN; ++j) a = fmaf(w[j], vcol[(size_t)j * G * E], a);
+          const int vs = G * E;
+          for (int j = 0; j < BN; j += 4) {          // BN is a multiple of 4
+            const float4 w4 = *reinterpret_cast<const float4*>(w + j);
+            a = fmaf(w4.x, vcol[j * vs], a);
+            a = fmaf(w4.y, vcol[(j + 1) * vs], a);
+            a = fmaf(w4.z, vcol[(j + 2) * vs], a);
+            a = fmaf(w4.w, vcol[(j + 3) * vs], a);
+          }
           acc[u] = a;
         }
       }
