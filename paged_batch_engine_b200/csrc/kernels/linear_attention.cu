@@ -5,10 +5,11 @@
 // per-request table, is read at the start of a request's rows of this step and written back
 // at their end; the step function zeroes it before a request's first tokens.
 //
-// One warp per (request, head, slice of value columns).  A lane owns one value column e and
-// holds S[:, e] in registers (or, for D beyond 128, PARTS lanes share a column and each holds
-// D / PARTS of it); per token the warp stages q_t and k_t in shared memory, every lane updates
-// its column and takes its dot product with q_t.  The next token's q, k and v are fetched
+// One block per (request, head, slice of value columns).  A thread owns (a share of) one value
+// column e and holds S[:, e] in registers: all of it for D up to 32, else PARTS neighbouring
+// lanes hold D / PARTS elements each; per token the block stages q_t and k_t in shared memory
+// (two buffers, one barrier a token), every thread updates its share and takes its part of the
+// dot product with q_t, and the parts are added by shuffles.  The token after next is fetched
 // while the current one is computed.  Prompt portions and single decoded tokens take the same
 // path: a request brings q_len rows.
 //
@@ -46,19 +47,25 @@ struct LinAttnParams {
   int act;                  // 1: silu on q, k and v
 };
 
-__device__ __forceinline__ float act_of(float x, int act) { return act ? x / (1.0f + expf(-x)) : x; }
+// silu with the fast exponential and division (errors of a few units in the last place of float32)
+__device__ __forceinline__ float act_of(float x, int act) { return act ? __fdividef(x, 1.0f + __expf(-x)) : x; }
 
-// DPT: state elements a lane holds (its share of D); PARTS lanes share one value column
-template <typename T, int DPT, int PARTS>
-__global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
-  constexpr int COLS = 32 / PARTS;             // value columns a warp covers
+// DPT: state elements a thread holds (its share of D); PARTS threads share one value column;
+// WARPS warps a block, which stage q_t and k_t once for all of them
+template <typename T, int DPT, int PARTS, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnParams p) {
+  constexpr int NT = 32 * WARPS;
+  constexpr int COLS = NT / PARTS;             // value columns a block covers
   constexpr int DMAX = DPT * PARTS;
-  __shared__ __align__(16) float qs[DMAX], ks[DMAX];
+  // a part's DPT elements are followed by four floats of padding: the PARTS lanes of a column read
+  // their own parts at once, 16 bytes each, and would otherwise all start in the same bank
+  constexpr int PSTRIDE = PARTS > 1 ? DPT + 4 : DPT;
+  __shared__ __align__(16) float qs[2][PARTS * PSTRIDE], ks[2][PARTS * PSTRIDE];
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
-  const int lane = threadIdx.x;
-  const int part = lane % PARTS, col = lane / PARTS;
+  const int tid = threadIdx.x;
+  const int part = tid % PARTS, col = tid / PARTS;
   const int e = blockIdx.z * COLS + col;
   const int D = p.D, E = p.E, H = p.H;
   int n, t0, src, dst;
@@ -72,7 +79,7 @@ __global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
   }
   if (n <= 0) return;
   const bool live = e < E;
-  const int d0 = part * DPT;                   // this lane's first state row
+  const int d0 = part * DPT;                   // this thread's first state row
   const size_t per_head = (size_t)D * E;
   auto place = [&](int v) -> float* {
     if (v == -1) return nullptr;
@@ -87,38 +94,45 @@ __global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
   const T* qp = (const T*)p.q + (size_t)h * D;
   const T* kp = (const T*)p.k + (size_t)h * D;
   const T* vp = (const T*)p.v + (size_t)h * E;
-  constexpr int PER = (DMAX + 31) / 32;        // q and k elements a lane fetches per token
+  constexpr int PER = (DMAX + NT - 1) / NT;    // q and k elements a thread fetches per token
   float qn[PER], kn[PER], vn;
   auto fetch = [&](int t) {
     const size_t row = (size_t)(t0 + t) * p.ld;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int d = lane + i * 32;
+      const int d = tid + i * NT;
       qn[i] = d < D ? act_of(to_float(qp[row + d]), p.act) : 0.f;
       kn[i] = d < D ? act_of(to_float(kp[row + d]), p.act) * p.k_scale : 0.f;
     }
     vn = live ? act_of(to_float(vp[row + e]), p.act) : 0.f;
   };
-  fetch(0);
-  for (int t = 0; t < n; ++t) {
-    __syncwarp();
+  auto stage = [&](int buf) {
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int d = lane + i * 32;
+      const int d = tid + i * NT;
       if (d < DMAX) {
-        qs[d] = qn[i];
-        ks[d] = kn[i];
+        const int at = (d / DPT) * PSTRIDE + (d % DPT);
+        qs[buf][at] = qn[i];
+        ks[buf][at] = kn[i];
       }
     }
-    const float v = vn;
-    __syncwarp();
-    if (t + 1 < n) fetch(t + 1);
+  };
+  fetch(0);
+  stage(0);
+  float v = vn;
+  if (n > 1) fetch(1);
+  for (int t = 0; t < n; ++t) {
+    // token t is staged in buffer t & 1 (and visible after this barrier); token t + 1 waits in
+    // registers and is staged into the other buffer, which token t - 1's readers have left
+    if (WARPS > 1) __syncthreads(); else __syncwarp();
+    const float* kb = ks[t & 1] + part * PSTRIDE;
+    const float* qb = qs[t & 1] + part * PSTRIDE;
     float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;       // four chains: the sum's latency does not bind
     if (p.out) {
 #pragma unroll
       for (int i = 0; i < DPT; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(ks + d0 + i);
-        const float4 q4 = *reinterpret_cast<const float4*>(qs + d0 + i);
+        const float4 k4 = *reinterpret_cast<const float4*>(kb + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qb + i);
         S[i] = fmaf(lam, S[i], k4.x * v);
         o0 = fmaf(S[i], q4.x, o0);
         S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
@@ -131,7 +145,7 @@ __global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
     } else {                                             // a chunk's own contribution only
 #pragma unroll
       for (int i = 0; i < DPT; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(ks + d0 + i);
+        const float4 k4 = *reinterpret_cast<const float4*>(kb + i);
         S[i] = fmaf(lam, S[i], k4.x * v);
         S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
         S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
@@ -142,6 +156,11 @@ __global__ void __launch_bounds__(32) linear_attention_kernel(LinAttnParams p) {
 #pragma unroll
     for (int m = 1; m < PARTS; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
     if (p.out && live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = o;
+    if (t + 1 < n) {
+      stage((t + 1) & 1);
+      v = vn;
+      if (t + 2 < n) fetch(t + 2);
+    }
   }
   if (live && st) {
 #pragma unroll
@@ -179,22 +198,24 @@ __global__ void chunk_scan_kernel(ScanParams p) {
   }
 }
 
-template <typename T, int DPT, int PARTS>
+template <typename T, int DPT, int PARTS, int WARPS>
 void launch_la(const LinAttnParams& p, int R, cudaStream_t stream) {
-  constexpr int COLS = 32 / PARTS;
+  constexpr int COLS = 32 * WARPS / PARTS;
   dim3 grid(R, p.H, (p.E + COLS - 1) / COLS);
-  launch_k(linear_attention_kernel<T, DPT, PARTS>, grid, 32, 0, stream, p);
+  launch_k(linear_attention_kernel<T, DPT, PARTS, WARPS>, grid, 32 * WARPS, 0, stream, p);
 }
 
+// 32 state elements a thread (16 for the narrowest keys); wider keys are shared by 2 to 16 threads
+// of a warp, and from 4 on a block has four warps that stage a token's q and k together.
 template <typename T>
 int dispatch_la(const LinAttnParams& p, int R, cudaStream_t stream) {
   const int D = p.D;
-  if (D <= 16) launch_la<T, 16, 1>(p, R, stream);
-  else if (D <= 32) launch_la<T, 32, 1>(p, R, stream);
-  else if (D <= 64) launch_la<T, 64, 1>(p, R, stream);
-  else if (D <= 128) launch_la<T, 128, 1>(p, R, stream);
-  else if (D <= 256) launch_la<T, 128, 2>(p, R, stream);
-  else if (D <= 512) launch_la<T, 128, 4>(p, R, stream);
+  if (D <= 16) launch_la<T, 16, 1, 1>(p, R, stream);
+  else if (D <= 32) launch_la<T, 32, 1, 1>(p, R, stream);
+  else if (D <= 64) launch_la<T, 32, 2, 1>(p, R, stream);
+  else if (D <= 128) launch_la<T, 32, 4, 4>(p, R, stream);
+  else if (D <= 256) launch_la<T, 32, 8, 4>(p, R, stream);
+  else if (D <= 512) launch_la<T, 32, 16, 4>(p, R, stream);
   else return (int)cudaErrorInvalidValue;
   return launch_status();
 }

@@ -18,12 +18,25 @@
 //   heads are needed before any value is weighted, hence the two passes; the scores are
 //   computed by the same arithmetic in both, so the maximum of pass 1 is exact in pass 2.
 //   All arithmetic is float32.
+//
+// Compile with -DPBE_PA_F32=1 for float32 tensors, 0 for bfloat16: a library holds one of them.
 #include "common.cuh"
 #include "pdl.cuh"
 
 using namespace pbe;
 
+#ifndef PBE_PA_F32
+#error "PBE_PA_F32 must be defined (1: float32, 0: bfloat16)"
+#endif
+
 namespace {
+#if PBE_PA_F32
+using PaT = float;
+constexpr int PA_DTYPE = PBE_F32;
+#else
+using PaT = __nv_bfloat16;
+constexpr int PA_DTYPE = PBE_BF16;
+#endif
 // ------------------------------------------------------------------ qk_prepare
 struct QkPrepParams {
   const void* q;            // row 0 of each inside the projection, row stride ld elements
@@ -176,6 +189,12 @@ struct PoolAttnParams {
   int bt_tok_stride, bt_pool_stride;
   int H, G, D, E, page_tokens, window, pool, BN;
   float scale;
+  // the keys of a row tile cut into splits of `split_tiles` key tiles, a block each (grid.y):
+  int split_tiles, splits;
+  float* part_ml;           // [tiles][splits][BM * H][2]: maximum and sum of each split
+  float* stats;             // [tiles][BM * H][2]: the same over all splits
+  float* part_o;            // [tiles][splits][BM * H * E]: a split's share of the output
+  int mode;                 // 0, 1 or 2: see the kernel
 };
 
 constexpr int PA_THREADS = 256;
@@ -240,8 +259,14 @@ __device__ __forceinline__ void load_tile(float* dst, int stride, const T* src, 
   }
 }
 
+// MODE 0: a block walks all key tiles of its row tile twice (statistics, then values).
+// MODE 1: a block walks its split of the key tiles once and leaves the split's statistics.
+// MODE 2: a block takes the statistics over all splits (made by pa_combine_kernel), walks its
+//         split and leaves its share of the output; the shares are plain addends, since every
+//         probability is already normalised (pa_sum_kernel adds them).
 template <typename T, int BM>
 __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnParams p) {
+  const int MODE = p.mode;
   extern __shared__ __align__(16) float smem[];
   const int H = p.H, G = p.G, D = p.D, E = p.E, PT = p.page_tokens, BN = p.BN;
   const int rep = H / G;
@@ -273,21 +298,44 @@ __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnPa
   const int32_t* bt_tok = p.bt_tok + (size_t)r * p.bt_tok_stride;
   const int32_t* bt_pool = p.bt_pool ? p.bt_pool + (size_t)r * p.bt_pool_stride : nullptr;
 
+  if (MODE != 0 && (int)blockIdx.y * p.split_tiles >= pool_tiles + tok_tiles) {
+    // a split beyond this row tile's keys: neutral statistics, a share of zeros
+    if (MODE == 1) {
+      float* ml = p.part_ml + (((size_t)blockIdx.x * p.splits + blockIdx.y) * BM * H) * 2;
+      for (int i = threadIdx.x; i < BM * H; i += blockDim.x) {
+        ml[2 * i] = -INFINITY;
+        ml[2 * i + 1] = 0.f;
+      }
+    } else {
+      float* po = p.part_o + ((size_t)blockIdx.x * p.splits + blockIdx.y) * BM * H * E;
+      for (int i = threadIdx.x; i < BM * H * E; i += blockDim.x) po[i] = 0.f;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < BM * H * D; i += blockDim.x) {
     const int row = i / (H * D), c = i - row * (H * D);
     Qs[i] = row < rows ? to_float(((const T*)p.q)[(size_t)(row0 + row) * H * D + c]) * p.scale : 0.f;
   }
   for (int i = threadIdx.x; i < BM * H; i += blockDim.x) {
-    Ms[i] = -INFINITY;
-    Ls[i] = 0.f;
+    if (MODE == 2) {
+      const float* st = p.stats + ((size_t)blockIdx.x * BM * H + i) * 2;
+      Ms[i] = st[0];
+      Ls[i] = st[1];
+    } else {
+      Ms[i] = -INFINITY;
+      Ls[i] = 0.f;
+    }
   }
   float acc[PA_ACC];
 #pragma unroll
   for (int i = 0; i < PA_ACC; ++i) acc[i] = 0.f;
   const int n_out = BM * H * E;
+  const int all_tiles = pool_tiles + tok_tiles;
+  const int kt_lo = MODE == 0 ? 0 : min(all_tiles, (int)blockIdx.y * p.split_tiles);
+  const int kt_hi = MODE == 0 ? all_tiles : min(all_tiles, kt_lo + p.split_tiles);
 
-  for (int pass = 0; pass < 2; ++pass) {
-    for (int kt = 0; kt < pool_tiles + tok_tiles; ++kt) {
+  for (int pass = (MODE == 2 ? 1 : 0); pass < (MODE == 1 ? 1 : 2); ++pass) {
+    for (int kt = kt_lo; kt < kt_hi; ++kt) {
       const bool pooled = kt < pool_tiles;
       const int first = pooled ? kt * BN : tok_lo + (kt - pool_tiles) * BN;    // block or token index of key 0
       const int limit = pooled ? nb_max : pos_last + 1;
@@ -393,24 +441,93 @@ __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnPa
       }
     }
   }
+  if (MODE == 1) {
+    __syncthreads();
+    float* ml = p.part_ml + (((size_t)blockIdx.x * p.splits + blockIdx.y) * BM * H) * 2;
+    for (int i = threadIdx.x; i < BM * H; i += blockDim.x) {
+      ml[2 * i] = Ms[i];
+      ml[2 * i + 1] = Ls[i];
+    }
+  } else if (MODE == 2) {
+    float* po = p.part_o + ((size_t)blockIdx.x * p.splits + blockIdx.y) * n_out;
 #pragma unroll
-  for (int u = 0; u < PA_ACC; ++u) {
-    const int o = threadIdx.x + u * PA_THREADS;
-    if (o < n_out) {
-      const int c = o % (H * E), row = o / (H * E);
-      if (row < rows) ((T*)p.out)[(size_t)(row0 + row) * H * E + c] = from_float<T>(acc[u]);
+    for (int u = 0; u < PA_ACC; ++u) {
+      const int o = threadIdx.x + u * PA_THREADS;
+      if (o < n_out) po[o] = acc[u];
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < PA_ACC; ++u) {
+      const int o = threadIdx.x + u * PA_THREADS;
+      if (o < n_out) {
+        const int c = o % (H * E), row = o / (H * E);
+        if (row < rows) ((T*)p.out)[(size_t)(row0 + row) * H * E + c] = from_float<T>(acc[u]);
+      }
     }
   }
 }
 
+// The statistics of a row tile over all its splits: m = max m_s, l = sum l_s e^(m_s - m).
+__global__ void pa_combine_kernel(const float* part_ml, float* stats, int splits, int per_tile) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= per_tile) return;
+  const float* ml = part_ml + ((size_t)blockIdx.x * splits * per_tile + i) * 2;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[(size_t)s * per_tile * 2]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = ml[(size_t)s * per_tile * 2];
+    if (ms != -INFINITY) l += ml[(size_t)s * per_tile * 2 + 1] * expf(ms - m);
+  }
+  float* st = stats + ((size_t)blockIdx.x * per_tile + i) * 2;
+  st[0] = m;
+  st[1] = l;
+}
+
+// out = sum over the splits of their shares, in split order.
+template <typename T>
+__global__ void pa_sum_kernel(const float* part_o, void* out, const int32_t* tiles, int splits, int n_out, int HE) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int o = blockIdx.y * blockDim.x + threadIdx.x;
+  if (o >= n_out) return;
+  const int32_t* tile = tiles + (size_t)blockIdx.x * 3;
+  const int row = o / HE, c = o - row * HE;
+  if (row >= tile[2]) return;
+  const float* po = part_o + (size_t)blockIdx.x * splits * n_out + o;
+  float a = 0.f;
+  for (int s = 0; s < splits; ++s) a += po[(size_t)s * n_out];
+  ((T*)out)[(size_t)(tile[1] + row) * HE + c] = from_float<T>(a);
+}
+
 template <typename T, int BM>
-int launch_pa(const PoolAttnParams& p, int n_tiles, size_t smem, cudaStream_t stream) {
+int launch_pa(PoolAttnParams p, int mode, int n_tiles, size_t smem, cudaStream_t stream) {
   static size_t opted = 0;
   if (smem > 48 * 1024 && opted < smem) {
     cudaFuncSetAttribute(pooled_attention_kernel<T, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     opted = smem;
   }
-  launch_k(pooled_attention_kernel<T, BM>, n_tiles, PA_THREADS, smem, stream, p);
+  p.mode = mode;
+  dim3 grid(n_tiles, mode == 0 ? 1 : p.splits);
+  launch_k(pooled_attention_kernel<T, BM>, grid, PA_THREADS, smem, stream, p);
+  return launch_status();
+}
+
+template <typename T, int BM>
+int run_pa(const PoolAttnParams& p, int n_tiles, size_t smem, cudaStream_t stream) {
+  if (p.splits <= 1) return launch_pa<T, BM>(p, 0, n_tiles, smem, stream);
+  int rc = launch_pa<T, BM>(p, 1, n_tiles, smem, stream);
+  if (rc) return rc;
+  const int per_tile = BM * p.H;
+  launch_k(pa_combine_kernel, dim3(n_tiles, (per_tile + 127) / 128), 128, 0, stream, (const float*)p.part_ml, p.stats,
+           p.splits, per_tile);
+  if ((rc = launch_status())) return rc;
+  if ((rc = launch_pa<T, BM>(p, 2, n_tiles, smem, stream))) return rc;
+  const int n_out = BM * p.H * p.E;
+  launch_k(pa_sum_kernel<T>, dim3(n_tiles, (n_out + 255) / 256), 256, 0, stream, (const float*)p.part_o, p.out, p.tiles,
+           p.splits, n_out, p.H * p.E);
   return launch_status();
 }
 
@@ -431,8 +548,8 @@ PBE_EXPORT int pbe_qk_prepare(const void* q, const void* k, const void* v, int l
   QkPrepParams p{q, k, v, ld, q_gain, k_gain, inv_freq, positions, slots, q_out, k_pages, v_pages,
                  H, G, D, E, rot, page_tokens, eps};
   const int threads = (H + G) * D >= 2048 ? 256 : 128;
-  if (dtype == PBE_F32) launch_k(qk_prepare_kernel<float>, T, threads, 0, stream, p);
-  else launch_k(qk_prepare_kernel<__nv_bfloat16>, T, threads, 0, stream, p);
+  if (dtype != PA_DTYPE) return (int)cudaErrorInvalidValue;
+  launch_k(qk_prepare_kernel<PaT>, T, threads, 0, stream, p);
   return launch_status();
 }
 
@@ -445,15 +562,22 @@ PBE_EXPORT int pbe_pool_blocks(const void* k_tok, const void* v_tok, void* k_poo
                G, D, E, page_tokens, pool};
   dim3 grid(T, G);
   const int threads = D + E >= 256 ? 256 : (D + E >= 128 ? 128 : 64);
-  if (dtype == PBE_F32) launch_k(pool_blocks_kernel<float>, grid, threads, 0, stream, p);
-  else launch_k(pool_blocks_kernel<__nv_bfloat16>, grid, threads, 0, stream, p);
+  if (dtype != PA_DTYPE) return (int)cudaErrorInvalidValue;
+  launch_k(pool_blocks_kernel<PaT>, grid, threads, 0, stream, p);
   return launch_status();
 }
 
-// The largest row tile (1, 2, 4, 8 or 16) whose outputs fit a block's accumulators.
+// Keys per key tile for a row tile of that many rows (what the launcher will choose).
+PBE_EXPORT int pbe_pooled_attention_key_tile(int tile_rows, int H, int G, int D, int E) {
+  int BN = 32;
+  while (BN > 4 && pa_smem(tile_rows, BN, H, G, D, E) > 200 * 1024) BN >>= 1;
+  return BN;
+}
+
+// The largest row tile (1, 4 or 16) whose outputs fit a block's accumulators.
 PBE_EXPORT int pbe_pooled_attention_tile_rows(int H, int E, int want) {
   int bm = 16;
-  while (bm > 1 && (bm > want || (long long)bm * H * E > (long long)PA_ACC * PA_THREADS)) bm >>= 1;
+  while (bm > 1 && (bm > want || (long long)bm * H * E > (long long)PA_ACC * PA_THREADS)) bm >>= 2;
   return (long long)bm * H * E > (long long)PA_ACC * PA_THREADS ? 0 : bm;
 }
 
@@ -462,7 +586,8 @@ PBE_EXPORT int pbe_pooled_attention(const void* q, const void* k_tok, const void
                                     int n_tiles, int tile_rows, const int32_t* q_start, const int32_t* q_len,
                                     const int32_t* seq_len, const int32_t* bt_tok, int bt_tok_stride,
                                     const int32_t* bt_pool, int bt_pool_stride, int H, int G, int D, int E,
-                                    int page_tokens, int window, int pool, float scale, int dtype,
+                                    int page_tokens, int window, int pool, float scale, int dtype, int splits,
+                                    int split_tiles, float* part_ml, float* stats, float* part_o,
                                     cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (H % G || (long long)tile_rows * H * E > (long long)PA_ACC * PA_THREADS) return (int)cudaErrorInvalidValue;
@@ -471,14 +596,13 @@ PBE_EXPORT int pbe_pooled_attention(const void* q, const void* k_tok, const void
   const size_t smem = pa_smem(tile_rows, BN, H, G, D, E);
   if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
   PoolAttnParams p{q, k_tok, v_tok, k_pool, v_pool, out, talk, tiles, q_start, q_len, seq_len, bt_tok, bt_pool,
-                   bt_tok_stride, bt_pool_stride, H, G, D, E, page_tokens, window, pool, BN, scale};
-#define PBE_PA(BM)                                                                              \
-  case BM:                                                                                      \
-    return dtype == PBE_F32 ? launch_pa<float, BM>(p, n_tiles, smem, stream)                    \
-                            : launch_pa<__nv_bfloat16, BM>(p, n_tiles, smem, stream);
+                   bt_tok_stride, bt_pool_stride, H, G, D, E, page_tokens, window, pool, BN, scale,
+                   split_tiles, splits, part_ml, stats, part_o, 0};
+  if (dtype != PA_DTYPE) return (int)cudaErrorInvalidValue;
   switch (tile_rows) {
-    PBE_PA(1) PBE_PA(2) PBE_PA(4) PBE_PA(8) PBE_PA(16)
+    case 1: return run_pa<PaT, 1>(p, n_tiles, smem, stream);
+    case 4: return run_pa<PaT, 4>(p, n_tiles, smem, stream);
+    case 16: return run_pa<PaT, 16>(p, n_tiles, smem, stream);
     default: return (int)cudaErrorInvalidValue;
   }
-#undef PBE_PA
 }

@@ -291,6 +291,11 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: t
 
 
 # ------------------------------------------------------------------ window + pooled blocks attention
+def _pa_defines(dtype: torch.dtype) -> dict:
+    """The pooled attention library of a dtype (one library per dtype, built when first asked for)."""
+    return {"PBE_PA_F32": 1 if dtype == torch.float32 else 0}
+
+
 def qk_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_gain: Optional[torch.Tensor],
                k_gain: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int,
                positions: torch.Tensor, slots: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
@@ -322,7 +327,7 @@ def qk_prepare(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_gain: Option
             raise KernelError("qk_prepare: pages must be [page, kv_head, page_tokens, width] in the activations' dtype")
     q_out = torch.empty((T, heads * D), dtype=q.dtype, device=q.device)
     fn = _fn("pooled_attention", "pbe_qk_prepare", [c_void_p, c_void_p, c_void_p, c_int] + [c_void_p] * 8 +
-             [c_int] * 7 + [c_float, c_int, c_void_p])
+             [c_int] * 7 + [c_float, c_int, c_void_p], _pa_defines(q.dtype))
     _check(fn(_ptr(q), _ptr(k), _ptr(v), ld, _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq), _ptr(positions), _ptr(slots),
               _ptr(q_out), _ptr(k_pages), _ptr(v_pages), T, heads, kv_heads, D, E,
               rotary_dim if inv_freq is not None else 0, page_tokens, float(eps), _dtype_code(q), _stream()),
@@ -341,26 +346,48 @@ def pool_blocks(k_tok, v_tok, k_pool, v_pool, positions, request_of_row, bt_tok,
     if tuple(k_pool.shape[1:]) != tuple(k_tok.shape[1:]) or tuple(v_pool.shape[1:]) != tuple(v_tok.shape[1:]) \
             or k_tok.shape[2] != page_tokens or len({k_tok.dtype, v_tok.dtype, k_pool.dtype, v_pool.dtype}) != 1:
         raise KernelError("pool_blocks: token pages and pooled pages differ in geometry or dtype")
-    fn = _fn("pooled_attention", "pbe_pool_blocks", [c_void_p] * 7 + [c_int, c_void_p] + [c_int] * 8 + [c_void_p])
+    fn = _fn("pooled_attention", "pbe_pool_blocks", [c_void_p] * 7 + [c_int, c_void_p] + [c_int] * 8 + [c_void_p],
+             _pa_defines(k_tok.dtype))
     _check(fn(_ptr(k_tok), _ptr(v_tok), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(request_of_row),
               _ptr(bt_tok), bt_tok.shape[1], _ptr(bt_pool), bt_pool.shape[1], T, G, D, E, page_tokens, int(pool),
               _dtype_code(k_tok), _stream()), "pool_blocks")
 
 
-def pooled_attention_tile_rows(heads: int, value_dim: int, want: int) -> int:
-    fn = _fn("pooled_attention", "pbe_pooled_attention_tile_rows", [c_int, c_int, c_int])
+def pooled_attention_tile_rows(heads: int, value_dim: int, want: int, dtype: torch.dtype = torch.bfloat16) -> int:
+    fn = _fn("pooled_attention", "pbe_pooled_attention_tile_rows", [c_int, c_int, c_int], _pa_defines(dtype))
     rows = fn(heads, value_dim, want)
     if rows <= 0:
         raise KernelError(f"pooled attention: {heads} heads x {value_dim} values a row are beyond the kernel")
     return rows
 
 
+PA_SPLIT_TILES = 4        # key tiles a block of the split form walks at least
+PA_MAX_SPLITS = 64        # blocks per row tile at most
+PA_FEW_TILES = 96         # row tiles below which the keys are split over more blocks
+
+
+def pooled_attention_splits(num_tiles: int, tile_rows: int, most_keys: int, heads: int, kv_heads: int, key_dim: int,
+                            value_dim: int, dtype: torch.dtype = torch.bfloat16):
+    """(blocks per row tile, key tiles a block walks): (1, 0) when the step's row tiles fill the
+    GPU by themselves, else the longest row's key tiles in groups of at least ``PA_SPLIT_TILES``,
+    at most ``PA_MAX_SPLITS`` groups."""
+    if num_tiles >= PA_FEW_TILES:
+        return 1, 0
+    fn = _fn("pooled_attention", "pbe_pooled_attention_key_tile", [c_int] * 5, _pa_defines(dtype))
+    bn = fn(tile_rows, heads, kv_heads, key_dim, value_dim)
+    tiles = (most_keys + bn - 1) // bn + 2           # pooled and token tiles round up separately
+    per = max(PA_SPLIT_TILES, (tiles + PA_MAX_SPLITS - 1) // PA_MAX_SPLITS)
+    return max(1, (tiles + per - 1) // per), per
+
+
 def pooled_attention(q, k_tok, v_tok, k_pool, v_pool, talk, tiles, num_tiles: int, tile_rows: int, q_start, q_len,
                      seq_len, bt_tok, bt_pool, heads: int, kv_heads: int, scale: float, window: int, pool: int,
-                     page_tokens: int) -> torch.Tensor:
+                     page_tokens: int, splits: int = 1, split_tiles: int = 0) -> torch.Tensor:
     """Softmax attention of every row over the tokens of its window and the pooled blocks before
     it (one softmax), the probabilities mixed across heads by ``talk`` (float32 [H, H], row h
-    weighs the heads' probabilities for head h; None: no mixing).  Returns [T, heads * E]."""
+    weighs the heads' probabilities for head h; None: no mixing).  ``splits`` > 1: the keys of a
+    row tile are cut over that many blocks (statistics per split, their combination, the
+    normalised shares of the output, their sum).  Returns [T, heads * E]."""
     _need_cuda(q, k_tok, v_tok, k_pool, v_pool, talk, tiles, q_start, q_len, seq_len, bt_tok, bt_pool)
     _need_contiguous(q, k_tok, v_tok, k_pool, v_pool, talk, tiles, q_start, q_len, seq_len, bt_tok, bt_pool)
     T = q.shape[0]
@@ -372,13 +399,20 @@ def pooled_attention(q, k_tok, v_tok, k_pool, v_pool, talk, tiles, num_tiles: in
     if pool and (k_pool is None or bt_pool is None):
         raise KernelError("pooled_attention: pooled blocks need their pages and block table")
     out = torch.empty((T, heads * E), dtype=q.dtype, device=q.device)
+    part_ml = stats = part_o = None
+    if splits > 1:
+        per = tile_rows * heads
+        part_ml = torch.empty((num_tiles, splits, per, 2), dtype=torch.float32, device=q.device)
+        stats = torch.empty((num_tiles, per, 2), dtype=torch.float32, device=q.device)
+        part_o = torch.empty((num_tiles, splits, per * E), dtype=torch.float32, device=q.device)
     fn = _fn("pooled_attention", "pbe_pooled_attention",
              [c_void_p] * 8 + [c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p, c_int] + [c_int] * 7 +
-             [c_float, c_int, c_void_p])
+             [c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p], _pa_defines(q.dtype))
     _check(fn(_ptr(q), _ptr(k_tok), _ptr(v_tok), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(talk), _ptr(tiles),
               num_tiles, tile_rows, _ptr(q_start), _ptr(q_len), _ptr(seq_len), _ptr(bt_tok), bt_tok.shape[1],
               _ptr(bt_pool), bt_pool.shape[1] if bt_pool is not None else 0, heads, kv_heads, D, E, page_tokens,
-              int(window), int(pool or 0), float(scale), _dtype_code(q), _stream()), "pooled_attention")
+              int(window), int(pool or 0), float(scale), _dtype_code(q), int(splits), int(split_tiles), _ptr(part_ml),
+              _ptr(stats), _ptr(part_o), _stream()), "pooled_attention")
     return out
 
 

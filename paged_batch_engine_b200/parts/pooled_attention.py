@@ -76,7 +76,7 @@ class PooledWindowAttention(Mixer):
         return CompositeNeed.of(tokens=tokens, pooled=PagedNeed(pair, window=None, stride=self.pool))
 
     def kernel_libraries(self, dtype):
-        return [("pooled_attention", None)] + ops.gemm_libraries(dtype)
+        return [("pooled_attention", {"PBE_PA_F32": 1 if dtype == torch.float32 else 0})] + ops.gemm_libraries(dtype)
 
     # ---- tensors
     def param_specs(self, prefix):
@@ -123,14 +123,22 @@ class PooledWindowAttention(Mixer):
                 ops.pool_blocks(tok.k, tok.v, k_pool, v_pool, ctx.positions, ctx.request_of_row, gt.block_table,
                                 bt_pool, self.pool, ctx.page_tokens)
         if self._tile_rows is None:
-            self._tile_rows = ops.pooled_attention_tile_rows(H, E, 16)
+            self._tile_rows = ops.pooled_attention_tile_rows(H, E, 16, self.dtype)
         # decoded tokens only (always so in a captured step): a row a tile
         single = getattr(ctx, "captured", False) or int(ctx.q_len_host.max(initial=1)) == 1
         rows = 1 if single else self._tile_rows
         tiles, n_tiles = ctx.row_tiles(rows)
+        # few row tiles (decoded tokens, short portions): the keys are split over more blocks; a
+        # captured step is sized for the longest context its block tables can hold
+        if getattr(ctx, "captured", False):
+            longest = gt.block_table.shape[1] * ctx.page_tokens
+        else:
+            longest = int(ctx.seq_len_host.max(initial=1))
+        most_keys = min(longest, self.window + rows - 1) + (longest // self.pool if self.pool else 0)
+        splits, split_tiles = ops.pooled_attention_splits(n_tiles, rows, most_keys, H, G, D, E, self.dtype)
         out = ops.pooled_attention(q, tok.k, tok.v, k_pool, v_pool, self.talk, tiles, n_tiles, rows, ctx.q_start,
                                    ctx.q_len, ctx.seq_len, gt.block_table, bt_pool, H, G, self.scale, self.window,
-                                   self.pool, ctx.page_tokens)
+                                   self.pool, ctx.page_tokens, splits, split_tiles)
         return ops.linear(out, self.w_o, None, out_dtype=self.dtype, kind=2)
 
 
