@@ -114,7 +114,9 @@ class CacheStorage:
 
     def bytes_per_token(self) -> int:
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.layers) * sum(t.heads * t.width for t in g.tensors) * size for g in self.groups)
+        # a group of one entry per `stride` tokens costs a token that much less
+        return sum(-(-len(g.layers) * sum(t.heads * t.width for t in g.tensors) * size // max(1, g.stride))
+                   for g in self.groups)
 
     def zero_state(self, slots) -> None:
         """Zeroes the state rows of these request slots in every stateful layer (the step
