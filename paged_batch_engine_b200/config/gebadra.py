@@ -102,13 +102,22 @@ class GebadraConfig:
                 if mlp.get("kind", "dense") != "dense":
                     raise ConfigError(f"{where}.mlp.kind {mlp.get('kind')!r} is not supported (only 'dense')")
                 _positive(_need(mlp, "ff", where + ".mlp"), f"{where}.mlp.ff")
-            j = layer.get("weights_of")
-            if j is not None:
-                if not isinstance(j, int) or not 0 <= j < len(self.layers) or j == i \
-                        or self.layers[j].get("weights_of") is not None:
-                    raise ConfigError(f"{where}.weights_of must name another layer that has tensors of its own")
+            if layer.get("weights_of") is not None:
+                j = self.owner_of(i)
                 if self.layers[j]["type"] != kind:
                     raise ConfigError(f"{where}.weights_of names a layer of another type")
+
+    def owner_of(self, i: int) -> int:
+        """The layer whose tensors layer i runs: itself, or the layer its ``weights_of`` names (followed
+        through layers that name another in turn)."""
+        seen = {i}
+        while self.layers[i].get("weights_of") is not None:
+            j = self.layers[i]["weights_of"]
+            if not isinstance(j, int) or isinstance(j, bool) or not 0 <= j < len(self.layers) or j in seen:
+                raise ConfigError(f"layers[{i}].weights_of must name another layer that has tensors of its own")
+            seen.add(j)
+            i = j
+        return i
 
     @staticmethod
     def _check_linear(m: dict, where: str) -> None:
@@ -171,8 +180,7 @@ class GebadraConfig:
                 names=dict(mixer="mix.", feed_forward="mlp.", norm_mixer="norm1", norm_feed_forward="norm2",
                            streams_mixer="hc1.", streams_feed_forward="hc2."),
                 args=dict(streams=self.streams)))
-        run = tuple(RunStep(block=block_of[layer.get("weights_of", i) if layer.get("weights_of") is not None else i],
-                            cache_layer=i) for i, layer in enumerate(self.layers))
+        run = tuple(RunStep(block=block_of[self.owner_of(i)], cache_layer=i) for i in range(len(self.layers)))
         return ModelSpec(
             architecture="Gebadra", hidden_size=self.width, vocab_size=self.vocab, blocks=tuple(blocks),
             run_order=run, final_norm=norm, embedding_name="embed", final_norm_name="final.norm",

@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(PA_THREADS) pooled_attention_kernel(PoolAttnPa
   const int rep = H / G;
   const int KS = G * D + 1;                  // padded key row
   float* Qs = smem;                          // [BM][H * D], scaled
-  float* Ks = Qs + BM * H * D;               // [BN][KS]
+  float* Ks = Qs + ((BM * H * D + 3) & ~3);  // [BN][KS]; what follows stays on 16-byte boundaries
   float* Vs = Ks + BN * KS;                  // [BN][G * E]
   float* Ss = Vs + BN * G * E;               // [BM][H][BN] scores, then probabilities
   float* Ws = Ss + BM * H * BN;              // [BM][H][BN] mixed probabilities
@@ -532,7 +532,8 @@ int run_pa(const PoolAttnParams& p, int n_tiles, size_t smem, cudaStream_t strea
 }
 
 size_t pa_smem(int BM, int BN, int H, int G, int D, int E) {
-  size_t f = (size_t)BM * H * D + (size_t)BN * (G * D + 1) + (size_t)BN * G * E + 2 * (size_t)BM * H * BN +
+  size_t f = (((size_t)BM * H * D + 3) & ~(size_t)3) + (size_t)BN * (G * D + 1) + (size_t)BN * G * E +
+             2 * (size_t)BM * H * BN +
              2 * (size_t)BM * H + (size_t)H * H;
   f = (f + 1) & ~(size_t)1;
   return f * sizeof(float) + (size_t)BN * sizeof(long long);

@@ -39,6 +39,14 @@ def test_model_as_data_run_order_and_shared_tensors():
     assert not any(n.startswith("l2.") or n.startswith("l3.") for n in names)
 
 
+def test_a_layer_may_name_a_layer_that_names_another():
+    cfg = copy.deepcopy(GEB_A)
+    cfg["layers"].append(dict(cfg["layers"][2], weights_of=2))
+    _, typed = load_config(cfg)
+    spec = typed.model_spec()
+    assert [s.block for s in spec.run_order] == [0, 1, 0, 1, 0] and len(spec.blocks) == 2
+
+
 def test_no_streams_key_means_no_connection_tensors_and_null_mlp_no_feed_forward():
     _, cfg = load_config(GEB_B)
     model = build_model(cfg, torch.float32, "cpu")
@@ -60,7 +68,8 @@ def test_one_stream_given_still_has_its_tensors():
     (lambda c: c["layers"][0]["mixer"].__setitem__("decay", [0.5]), "one decay per head"),
     (lambda c: c["layers"][1]["mixer"]["left"].__setitem__("kv_heads", 3), "multiple of kv_heads"),
     (lambda c: c["layers"][2].__setitem__("weights_of", 1), "another type"),
-    (lambda c: c["layers"][3].__setitem__("weights_of", 2), "tensors of its own"),
+    (lambda c: c["layers"][3].__setitem__("weights_of", 3), "tensors of its own"),
+    (lambda c: c["layers"][1].__setitem__("weights_of", 3), "tensors of its own"),
     (lambda c: c["layers"][1]["mlp"].__setitem__("kind", "routed"), "not supported"),
     (lambda c: c.pop("width"), "lacks 'width'"),
     (lambda c: c.__setitem__("streams", 0), "streams"),

@@ -432,6 +432,38 @@ def test_greedy_generation_through_the_entry_point(folders):
             toks.append(got)
 
 
+def test_command_line_generates_greedily(folders):
+    cfg, _, page = GEBADRA["B"]
+    c, w = load_plain(folders["B"])
+    prompt = [7, 100, 33, 2, 150, 9, 81, 64, 5, 199, 12]
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "pbe-qwen"), folders["B"], "--prompt-ids",
+                        ",".join(map(str, prompt)), "--max-new-tokens", "6", "--dtype", "float32", "--ignore-eos",
+                        "--page-size", str(page), "--kv-cache-blocks-per-layer", "32", "--max-num-seqs", "2"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")][0]
+    toks = list(prompt)
+    for got in line["output_ids"]:
+        lg = pg.forward(c, w, toks)[-1]
+        top2 = lg.topk(2).values
+        if float(top2[0] - top2[1]) > 1e-4:
+            assert got == int(lg.argmax()), (len(toks), got, int(lg.argmax()))
+        toks.append(got)
+    assert len(line["output_ids"]) == 6
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 70, 72), (5, 33, 40), (8, 250, 104), (20, 70, 72), (3, 66, 100)])
+def test_projections_of_widths_that_divide_nothing(M, N, K):
+    """The fused projections of a model with odd sizes: every route of the engine's product."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(M * N)
+    x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    for dt, tol in ((torch.float32, 1e-4), (torch.bfloat16, 0.15)):
+        y = ops.linear(x.to(DEV).to(dt), w.to(DEV).to(dt), None, out_dtype=dt).float().cpu()
+        want = x.to(dt).double() @ w.to(dt).double().T
+        assert float((y.double() - want).abs().max()) <= tol, (dt, M, N, K)
+
+
 def test_trace_runner_program(folders, tmp_path):
     cfg, _, page = GEBADRA["A"]
     reqs = requests_for("A", cfg["vocab"])
