@@ -7,10 +7,10 @@
 //
 // One block per (request, head, slice of value columns).  A thread owns (a share of) one value
 // column e and holds S[:, e] in registers: all of it for D up to 32, else PARTS neighbouring
-// lanes hold D / PARTS elements each; per token the block stages q_t and k_t in shared memory
-// (two buffers, one barrier a token), every thread updates its share and takes its part of the
-// dot product with q_t, and the parts are added by shuffles.  The token after next is fetched
-// while the current one is computed.  Prompt portions and single decoded tokens take the same
+// lanes hold D / PARTS elements each; the block stages q and k of a batch of tokens in shared
+// memory (two buffers, one barrier a batch; a batch's loads are all in flight at once and the batch
+// after next is fetched while the current one is computed), every thread updates its share token
+// by token and takes its part of the dot product with q_t, and the parts are added by shuffles.  Prompt portions and single decoded tokens take the same
 // path: a request brings q_len rows.
 //
 // Long prompt portions are cut into chunks that run side by side (the launcher's work items):
@@ -51,8 +51,8 @@ struct LinAttnParams {
 __device__ __forceinline__ float act_of(float x, int act) { return act ? __fdividef(x, 1.0f + __expf(-x)) : x; }
 
 // DPT: state elements a thread holds (its share of D); PARTS threads share one value column;
-// WARPS warps a block, which stage q_t and k_t once for all of them
-template <typename T, int DPT, int PARTS, int WARPS>
+// WARPS warps a block, which stage q and k of TB tokens at a time for all of them
+template <typename T, int DPT, int PARTS, int WARPS, int TB>
 __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnParams p) {
   constexpr int NT = 32 * WARPS;
   constexpr int COLS = NT / PARTS;             // value columns a block covers
@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
   // a part's DPT elements are followed by four floats of padding: the PARTS lanes of a column read
   // their own parts at once, 16 bytes each, and would otherwise all start in the same bank
   constexpr int PSTRIDE = PARTS > 1 ? DPT + 4 : DPT;
-  __shared__ __align__(16) float qs[2][PARTS * PSTRIDE], ks[2][PARTS * PSTRIDE];
+  constexpr int ROW = PARTS * PSTRIDE;
+  __shared__ __align__(16) float qs[2][TB][ROW], ks[2][TB][ROW];
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
@@ -94,72 +95,89 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
   const T* qp = (const T*)p.q + (size_t)h * D;
   const T* kp = (const T*)p.k + (size_t)h * D;
   const T* vp = (const T*)p.v + (size_t)h * E;
-  constexpr int PER = (DMAX + NT - 1) / NT;    // q and k elements a thread fetches per token
-  float qn[PER], kn[PER], vn;
-  auto fetch = [&](int t) {
-    const size_t row = (size_t)(t0 + t) * p.ld;
+  constexpr int PER = (DMAX + NT - 1) / NT;    // q and k elements of a token a thread fetches
+  // a batch of TB tokens travels together: all its loads are in flight at once, and it waits in
+  // registers while the batch before it is computed
+  T qn[TB][PER], kn[TB][PER], vn[TB];
+  auto fetch = [&](int b) {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int d = tid + i * NT;
-      qn[i] = d < D ? act_of(to_float(qp[row + d]), p.act) : 0.f;
-      kn[i] = d < D ? act_of(to_float(kp[row + d]), p.act) * p.k_scale : 0.f;
+    for (int tt = 0; tt < TB; ++tt) {
+      const int t = b * TB + tt;
+      const bool ok = t < n;
+      const size_t row = (size_t)(t0 + (ok ? t : 0)) * p.ld;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int d = tid + i * NT;
+        qn[tt][i] = (ok && d < D) ? qp[row + d] : from_float<T>(0.f);
+        kn[tt][i] = (ok && d < D) ? kp[row + d] : from_float<T>(0.f);
+      }
+      vn[tt] = (ok && live) ? vp[row + e] : from_float<T>(0.f);
     }
-    vn = live ? act_of(to_float(vp[row + e]), p.act) : 0.f;
   };
+  float vcur[TB];
   auto stage = [&](int buf) {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int d = tid + i * NT;
-      if (d < DMAX) {
-        const int at = (d / DPT) * PSTRIDE + (d % DPT);
-        qs[buf][at] = qn[i];
-        ks[buf][at] = kn[i];
+    for (int tt = 0; tt < TB; ++tt) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int d = tid + i * NT;
+        if (d < DMAX) {
+          const int at = (d / DPT) * PSTRIDE + (d % DPT);
+          qs[buf][tt][at] = act_of(to_float(qn[tt][i]), p.act);
+          ks[buf][tt][at] = act_of(to_float(kn[tt][i]), p.act) * p.k_scale;
+        }
       }
+      vcur[tt] = act_of(to_float(vn[tt]), p.act);
     }
   };
+  const int nb = (n + TB - 1) / TB;
   fetch(0);
   stage(0);
-  float v = vn;
-  if (n > 1) fetch(1);
-  for (int t = 0; t < n; ++t) {
-    // token t is staged in buffer t & 1 (and visible after this barrier); token t + 1 waits in
-    // registers and is staged into the other buffer, which token t - 1's readers have left
+  if (nb > 1) fetch(1);
+  for (int b = 0; b < nb; ++b) {
+    // batch b is staged in buffer b & 1 (visible after this barrier); batch b + 1 waits in registers
+    // and is staged into the other buffer, which batch b - 1's readers have left
     if (WARPS > 1) __syncthreads(); else __syncwarp();
-    const float* kb = ks[t & 1] + part * PSTRIDE;
-    const float* qb = qs[t & 1] + part * PSTRIDE;
-    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;       // four chains: the sum's latency does not bind
-    if (p.out) {
 #pragma unroll
-      for (int i = 0; i < DPT; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kb + i);
-        const float4 q4 = *reinterpret_cast<const float4*>(qb + i);
-        S[i] = fmaf(lam, S[i], k4.x * v);
-        o0 = fmaf(S[i], q4.x, o0);
-        S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
-        o1 = fmaf(S[i + 1], q4.y, o1);
-        S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
-        o2 = fmaf(S[i + 2], q4.z, o2);
-        S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
-        o3 = fmaf(S[i + 3], q4.w, o3);
-      }
-    } else {                                             // a chunk's own contribution only
+    for (int tt = 0; tt < TB; ++tt) {
+      const int t = b * TB + tt;
+      if (t >= n) break;
+      const float* kb = ks[b & 1][tt] + part * PSTRIDE;
+      const float* qb = qs[b & 1][tt] + part * PSTRIDE;
+      const float v = vcur[tt];
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;       // four chains: the sum's latency does not bind
+      if (p.out) {
 #pragma unroll
-      for (int i = 0; i < DPT; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kb + i);
-        S[i] = fmaf(lam, S[i], k4.x * v);
-        S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
-        S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
-        S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kb + i);
+          const float4 q4 = *reinterpret_cast<const float4*>(qb + i);
+          S[i] = fmaf(lam, S[i], k4.x * v);
+          o0 = fmaf(S[i], q4.x, o0);
+          S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
+          o1 = fmaf(S[i + 1], q4.y, o1);
+          S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
+          o2 = fmaf(S[i + 2], q4.z, o2);
+          S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
+          o3 = fmaf(S[i + 3], q4.w, o3);
+        }
+      } else {                                             // a chunk's own contribution only
+#pragma unroll
+        for (int i = 0; i < DPT; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kb + i);
+          S[i] = fmaf(lam, S[i], k4.x * v);
+          S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
+          S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
+          S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
+        }
       }
+      float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+      for (int m = 1; m < PARTS; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+      if (p.out && live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = o;
     }
-    float o = (o0 + o1) + (o2 + o3);
-#pragma unroll
-    for (int m = 1; m < PARTS; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-    if (p.out && live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = o;
-    if (t + 1 < n) {
-      stage((t + 1) & 1);
-      v = vn;
-      if (t + 2 < n) fetch(t + 2);
+    if (b + 1 < nb) {
+      stage((b + 1) & 1);
+      if (b + 2 < nb) fetch(b + 2);
     }
   }
   if (live && st) {
@@ -198,24 +216,25 @@ __global__ void chunk_scan_kernel(ScanParams p) {
   }
 }
 
-template <typename T, int DPT, int PARTS, int WARPS>
+template <typename T, int DPT, int PARTS, int WARPS, int TB>
 void launch_la(const LinAttnParams& p, int R, cudaStream_t stream) {
   constexpr int COLS = 32 * WARPS / PARTS;
   dim3 grid(R, p.H, (p.E + COLS - 1) / COLS);
-  launch_k(linear_attention_kernel<T, DPT, PARTS, WARPS>, grid, 32 * WARPS, 0, stream, p);
+  launch_k(linear_attention_kernel<T, DPT, PARTS, WARPS, TB>, grid, 32 * WARPS, 0, stream, p);
 }
 
 // 32 state elements a thread (16 for the narrowest keys); wider keys are shared by 2 to 16 threads
-// of a warp, and from 4 on a block has four warps that stage a token's q and k together.
+// of a warp, and from 4 on a block has four warps that stage q and k together.  Tokens are staged
+// eight at a time (fewer where a token's keys are wide: the two buffers stay under 48 KB).
 template <typename T>
 int dispatch_la(const LinAttnParams& p, int R, cudaStream_t stream) {
   const int D = p.D;
-  if (D <= 16) launch_la<T, 16, 1, 1>(p, R, stream);
-  else if (D <= 32) launch_la<T, 32, 1, 1>(p, R, stream);
-  else if (D <= 64) launch_la<T, 32, 2, 1>(p, R, stream);
-  else if (D <= 128) launch_la<T, 32, 4, 4>(p, R, stream);
-  else if (D <= 256) launch_la<T, 32, 8, 4>(p, R, stream);
-  else if (D <= 512) launch_la<T, 32, 16, 4>(p, R, stream);
+  if (D <= 16) launch_la<T, 16, 1, 1, 8>(p, R, stream);
+  else if (D <= 32) launch_la<T, 32, 1, 1, 8>(p, R, stream);
+  else if (D <= 64) launch_la<T, 32, 2, 1, 8>(p, R, stream);
+  else if (D <= 128) launch_la<T, 32, 4, 4, 8>(p, R, stream);
+  else if (D <= 256) launch_la<T, 32, 8, 4, 4>(p, R, stream);
+  else if (D <= 512) launch_la<T, 32, 16, 4, 2>(p, R, stream);
   else return (int)cudaErrorInvalidValue;
   return launch_status();
 }

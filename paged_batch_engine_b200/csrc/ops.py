@@ -361,7 +361,8 @@ def pooled_attention_tile_rows(heads: int, value_dim: int, want: int, dtype: tor
     return rows
 
 
-PA_SPLIT_TILES = 4        # key tiles a block of the split form walks at least
+# key tiles a block of the split form walks at least (8 rows over 1,040 keys: 92 us with 1, 86 with 2, 135 with 4)
+PA_SPLIT_TILES = int(os.environ.get("PBE_PA_SPLIT_TILES", "2"))
 PA_MAX_SPLITS = 64        # blocks per row tile at most
 PA_FEW_TILES = 96         # row tiles below which the keys are split over more blocks
 

@@ -370,7 +370,8 @@ class StepContext:
     def recurrence_plan(self, chunk: int = RECURRENCE_CHUNK) -> RecurrencePlan:
         """The step's rows cut for a recurrence over each request's rows (made on first use, one
         copy to the device for all layers of the step)."""
-        plan = getattr(self, "_recurrence_plan", None)
+        plans = self.__dict__.setdefault("_recurrence_plans", {})
+        plan = plans.get(chunk)
         if plan is None:
             first, scan, second, entries = recurrence_plan_arrays(self.q_start_host, self.q_len_host,
                                                                   self.state_slots_host, chunk)
@@ -383,8 +384,8 @@ class StepContext:
                 dev = host.to(self.device, non_blocking=True)
                 a, b = len(first), len(first) + len(scan)
                 plan = RecurrencePlan(entries, dev[:a], a, dev[a:b], len(scan), dev[b:], len(second))
-                self._plan_host = host
-            self._recurrence_plan = plan
+                self.__dict__.setdefault("_plan_hosts", []).append(host)     # pinned until the step is done
+            plans[chunk] = plan
         return plan
 
     def row_tiles(self, tile_rows: int):
