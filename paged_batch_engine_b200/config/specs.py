@@ -65,6 +65,8 @@ class ModelSpec:
     max_position: int
     eos_token_ids: Tuple[int, ...] = ()
     residual_streams: int = 1      # parallel residual streams (all start as the embedding, summed at the end)
+    logit_scale: float = 1.0       # the head's output is multiplied by it
+    logit_softcap: Optional[float] = None   # c: logits <- c * tanh(logits / c), after the scale
 
     @property
     def num_cache_layers(self) -> int:

@@ -165,6 +165,109 @@ PBE_EXPORT int pbe_add_rmsnorm(float* residual, const void* delta, int delta_dty
   return launch_status();
 }
 
+// ---------------------------------------------------------------- residual add of two branches + two RMSNorms
+// A layer whose mixer and feed-forward read the same residual: x += (a + b) where a and b are the
+// two branches of the layer before (either may be absent), then y1 = g1 * x * r and y2 = g2 * x * r
+// with the one r = rsqrt(mean(x^2) + eps) both norms share.  g2 == nullptr: one output only.
+template <typename TD, typename TO>
+__global__ void add2_rmsnorm2_kernel(float* __restrict__ residual, const TD* __restrict__ delta_a,
+                                     const TD* __restrict__ delta_b, const float* __restrict__ gain1,
+                                     const float* __restrict__ gain2, TO* __restrict__ out1, TO* __restrict__ out2,
+                                     const int32_t* __restrict__ row_index, int d, float eps) {
+  __shared__ float red[33];
+  extern __shared__ __align__(16) float row[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = row_index ? row_index[r] : r;
+  float* res = residual + (size_t)src * d;
+  const TD* da = delta_a ? delta_a + (size_t)src * d : nullptr;
+  const TD* db = delta_b ? delta_b + (size_t)src * d : nullptr;
+  const bool write_back = row_index == nullptr && (da != nullptr || db != nullptr);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float add = 0.f;
+    if (da) add = to_float(da[i]);
+    if (db) add += to_float(db[i]);
+    const float v = res[i] + add;
+    row[i] = v;
+    ss += v * v;
+  }
+  const float scale = rsqrtf(block_sum(ss, red) / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = row[i];
+    if (write_back) res[i] = v;
+    out1[(size_t)r * d + i] = from_float<TO>((gain1[i] * v) * scale);
+    if (gain2) out2[(size_t)r * d + i] = from_float<TO>((gain2[i] * v) * scale);
+  }
+}
+
+PBE_EXPORT int pbe_add2_rmsnorm2(float* residual, const void* delta_a, const void* delta_b, int delta_dtype,
+                                 const float* gain1, const float* gain2, void* out1, void* out2, int out_dtype,
+                                 const int32_t* row_index, int num_rows, int d, float eps, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define LAUNCH2(TD, TO)                                                                            \
+  do {                                                                                             \
+    static size_t opted = 48 * 1024;                                                               \
+    if (smem > opted) {                                                                            \
+      cudaFuncSetAttribute(add2_rmsnorm2_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           200 * 1024);                                                            \
+      opted = 200 * 1024;                                                                          \
+    }                                                                                              \
+    launch_k(add2_rmsnorm2_kernel<TD, TO>, num_rows, threads, smem, stream, residual,              \
+             (const TD*)delta_a, (const TD*)delta_b, gain1, gain2, (TO*)out1, (TO*)out2, row_index, d, eps); \
+  } while (0)
+  if (delta_dtype == PBE_F32 && out_dtype == PBE_F32) LAUNCH2(float, float);
+  else if (delta_dtype == PBE_BF16 && out_dtype == PBE_BF16) LAUNCH2(__nv_bfloat16, __nv_bfloat16);
+  else if (delta_dtype == PBE_F32 && out_dtype == PBE_BF16) LAUNCH2(float, __nv_bfloat16);
+  else LAUNCH2(__nv_bfloat16, float);
+#undef LAUNCH2
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- relu(x)^2, and scaled soft-capped logits
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_float(in[i]), 0.f);
+    out[i] = from_float<T>(v * v);
+  }
+}
+
+PBE_EXPORT int pbe_relu_squared(const void* in, void* out, int dtype, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  size_t blocks = ((size_t)total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == PBE_F32) launch_k(relu_squared_kernel<float>, (int)blocks, 256, 0, stream, (const float*)in, (float*)out, (size_t)total);
+  else launch_k(relu_squared_kernel<__nv_bfloat16>, (int)blocks, 256, 0, stream, (const __nv_bfloat16*)in,
+                (__nv_bfloat16*)out, (size_t)total);
+  return launch_status();
+}
+
+// x <- x * scale, then (cap > 0) x <- cap * tanh(x / cap); float32 logits in place
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t total, float scale, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    x[i] = v;
+  }
+}
+
+PBE_EXPORT int pbe_scale_softcap(float* x, long long total, float scale, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  size_t blocks = ((size_t)total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_k(scale_softcap_kernel, (int)blocks, 256, 0, stream, x, (size_t)total, scale, cap);
+  return launch_status();
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 // in: [rows, 2*inter], gate in columns [0, inter), up in [inter, 2*inter); out [rows, inter].
 template <typename T>

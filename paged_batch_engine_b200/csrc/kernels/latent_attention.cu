@@ -1,0 +1,463 @@
+// Attention over a compressed latent: every token keeps one row [c | kr] in the paged cache (c: a
+// normed latent of `rank` values from which all heads' keys and values are linear maps; kr: one
+// rotated key part of `rot` values that all heads share).  Keys and values are never expanded:
+// the heads' key maps are applied to the queries instead and the heads' value maps to the
+// attention's output,
+//   score_h(i, j) = ((U_k,h^T q_h,i) . c_j + rope(q'_h,i) . kr_j) * scale,
+//   out_h(i) = U_v,h (sum_j w_h(i, j) c_j),
+// so that attention runs with one shared "key" row of rank + rot values and the first rank of
+// them as the "value".  The softmax may have a sink: a learned logit per head in the denominator
+// that has no key and no value.  Scores, weights and sums are float32.
+//
+//   latent_prepare   per token: RMS norms of the query latent and of c, rotation of kr, cache write
+//   head_product     out[t, h, :] = W_h a[t, h, :] per head (the absorbed queries; the values with
+//                    their sigmoid gate), float32 sums in a fixed order; optionally the rotated
+//                    query part is appended
+//   latent_attention causal attention of every row over its request's pages (same work list, row
+//                    packing and key splits as the engine's other paged attention kernels)
+//   latent_merge     the key splits' partial results and the sink into one result
+#include "attention_params.cuh"
+#include "common.cuh"
+#include "pdl.cuh"
+
+using namespace pbe;
+
+namespace {
+// ------------------------------------------------------------------------------------------------
+struct PrepareParams {
+  const void* proj;          // [T, ld]: the fused down projection
+  int ld;
+  int q_off, q_rank;         // columns of the query latent (q_rank 0: none)
+  int c_off, rank;           // columns of the key/value latent
+  int r_off, rot;            // columns of the shared rotated key part
+  const float* q_gain;       // [q_rank]
+  const float* c_gain;       // [rank]
+  const float* inv_freq;     // [rot_dims / 2]
+  int rot_dims;              // leading values of kr that are rotated, pairs (2i, 2i + 1)
+  const int32_t* positions;  // [T]
+  const int32_t* slots;      // [T] page * page_tokens + offset, negative: nothing is written
+  void* q_lat;               // [T, q_rank] normed query latent
+  void* cache;               // [pages * page_tokens, rank + rot] or null
+  float eps;
+};
+
+template <typename T>
+__global__ void latent_prepare_kernel(PrepareParams p) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const T* row = (const T*)p.proj + (size_t)t * p.ld;
+  if (p.q_rank > 0) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) {
+      const float v = to_float(row[p.q_off + i]);
+      ss += v * v;
+    }
+    const float scale = rsqrtf(block_sum(ss, red) / (float)p.q_rank + p.eps);
+    T* o = (T*)p.q_lat + (size_t)t * p.q_rank;
+    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x)
+      o[i] = from_float<T>((p.q_gain[i] * to_float(row[p.q_off + i])) * scale);
+  }
+  const int slot = p.slots ? p.slots[t] : -1;
+  if (p.cache == nullptr || slot < 0) return;
+  T* dst = (T*)p.cache + (size_t)slot * (p.rank + p.rot);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < p.rank; i += blockDim.x) {
+    const float v = to_float(row[p.c_off + i]);
+    ss += v * v;
+  }
+  const float scale = rsqrtf(block_sum(ss, red) / (float)p.rank + p.eps);
+  for (int i = threadIdx.x; i < p.rank; i += blockDim.x)
+    dst[i] = from_float<T>((p.c_gain[i] * to_float(row[p.c_off + i])) * scale);
+  const float pos = (float)p.positions[t];
+  for (int i = threadIdx.x; i < p.rot / 2; i += blockDim.x) {
+    const float u = to_float(row[p.r_off + 2 * i]), v = to_float(row[p.r_off + 2 * i + 1]);
+    float a = u, b = v;
+    if (2 * i + 1 < p.rot_dims) {
+      float sn, cs;
+      sincosf(pos * p.inv_freq[i], &sn, &cs);
+      a = u * cs - v * sn;
+      b = v * cs + u * sn;
+    }
+    dst[p.rank + 2 * i] = from_float<T>(a);
+    dst[p.rank + 2 * i + 1] = from_float<T>(b);
+  }
+  if ((p.rot & 1) && threadIdx.x == 0) dst[p.rank + p.rot - 1] = row[p.r_off + p.rot - 1];
+}
+
+// ------------------------------------------------------------------------------------------------
+// out[t, h, n] = sum_k a[t, h, k] * w[h][k * wk + n * wn]  for n < N, per head h
+struct HeadProductParams {
+  const void* a;             // element (row 0, head 0, 0); row stride lda, head stride ha
+  int lda, ha;
+  const void* w;             // head stride hw; element strides wk (along k) and wn (along n)
+  long long hw;
+  int wk, wn;
+  void* out;                 // row stride ldo, head stride ho
+  int ldo, ho;
+  int T, H, K, N;
+  // optional tail: out[t, h, N + i] = rope(a[t, h, K + i]) for i < rot (pairs (2i, 2i+1) of the first rot_dims)
+  int rot, rot_dims;
+  const float* inv_freq;
+  const int32_t* positions;
+  // optional gate: the result is multiplied by sigmoid(gate[t * ldg + h]); the gate has the weights' dtype
+  const void* gate;
+  int ldg;
+};
+
+constexpr int HP_TM = 16, HP_TN = 64, HP_TK = 32;
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256) head_product_kernel(HeadProductParams p) {
+  __shared__ float As[HP_TM][HP_TK + 1];
+  __shared__ float Ws[HP_TK][HP_TN + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.y;
+  const int t0 = blockIdx.x * HP_TM;
+  const int n0 = blockIdx.z * HP_TN;
+  const int tid = threadIdx.x;
+  const int tn = tid % HP_TN, tg = tid / HP_TN;           // column, and which four rows
+  const TA* a = (const TA*)p.a + (size_t)h * p.ha;
+  const TW* w = (const TW*)p.w + (size_t)h * p.hw;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < p.K; k0 += HP_TK) {
+    for (int idx = tid; idx < HP_TM * HP_TK; idx += 256) {
+      const int i = idx / HP_TK, k = idx - i * HP_TK;
+      const int t = t0 + i;
+      As[i][k] = (t < p.T && k0 + k < p.K) ? to_float(a[(size_t)t * p.lda + k0 + k]) : 0.f;
+    }
+    for (int idx = tid; idx < HP_TK * HP_TN; idx += 256) {
+      // the faster-running index follows the operand's unit stride
+      int k, n;
+      if (p.wn == 1) { k = idx / HP_TN; n = idx - k * HP_TN; } else { n = idx / HP_TK; k = idx - n * HP_TK; }
+      Ws[k][n] = (k0 + k < p.K && n0 + n < p.N) ? to_float(w[(size_t)(k0 + k) * p.wk + (size_t)(n0 + n) * p.wn]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < HP_TK; ++k) {
+      const float wv = Ws[k][tn];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] = fmaf(As[tg * 4 + j][k], wv, acc[j]);
+    }
+    __syncthreads();
+  }
+  const int n = n0 + tn;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int t = t0 + tg * 4 + j;
+    if (t >= p.T || n >= p.N) continue;
+    float v = acc[j];
+    if (p.gate) {
+      const float g = to_float(((const TW*)p.gate)[(size_t)t * p.ldg + h]);
+      v *= 1.0f / (1.0f + expf(-g));
+    }
+    ((TO*)p.out)[(size_t)t * p.ldo + (size_t)h * p.ho + n] = from_float<TO>(v);
+  }
+  if (p.rot > 0 && blockIdx.z == 0) {
+    for (int idx = tid; idx < HP_TM * (p.rot / 2); idx += 256) {
+      const int i = idx / (p.rot / 2), pr = idx - i * (p.rot / 2);
+      const int t = t0 + i;
+      if (t >= p.T) continue;
+      const TA* src = a + (size_t)t * p.lda + p.K;
+      const float u = to_float(src[2 * pr]), v = to_float(src[2 * pr + 1]);
+      float x = u, y = v;
+      if (2 * pr + 1 < p.rot_dims) {
+        float sn, cs;
+        sincosf((float)p.positions[t] * p.inv_freq[pr], &sn, &cs);
+        x = u * cs - v * sn;
+        y = v * cs + u * sn;
+      }
+      TO* dst = (TO*)p.out + (size_t)t * p.ldo + (size_t)h * p.ho + p.N;
+      dst[2 * pr] = from_float<TO>(x);
+      dst[2 * pr + 1] = from_float<TO>(y);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+struct LatentAttnParams {
+  AttnParams a;              // q: float32 [T, H, dk]; k_cache: [page][page_tokens][dk]; out: float32 [T, H, dv];
+                             // num_kv_heads 1, tile_rows a multiple of 16
+  const float* sink;         // [H] or null
+  int dk, dv;                // width of a cache row; its leading dv values are the value
+};
+
+constexpr int LA_BM = 16;    // packed rows (row x head) a block
+constexpr int LA_BN = 32;    // keys a tile, one per lane
+constexpr int LA_WARPS = 4;
+constexpr int LA_RPW = LA_BM / LA_WARPS;
+
+template <typename T, int DPL>
+__global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(LatentAttnParams lp) {
+  extern __shared__ __align__(16) float smem[];
+  const AttnParams& p = lp.a;
+  const int DK = lp.dk, DV = lp.dv;
+  const int KS = DK | 1;                 // odd row stride: a key per lane without bank conflicts
+  float* Qs = smem;                      // [LA_BM][DK]
+  float* Ks = Qs + LA_BM * DK;           // [LA_BN][KS]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int32_t* work = p.work + (size_t)blockIdx.x * 4;
+  const int r = work[0];
+  if (r < 0) return;
+  const int split = work[2], nsplit = work[3];
+  const int H = p.num_heads, G = H, P = p.page_tokens;
+  const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
+  const int n_packed = nq * G;
+  const int pr0 = work[1] * p.tile_rows + blockIdx.y * LA_BM;
+  if (pr0 >= n_packed || blockIdx.y * LA_BM >= p.tile_rows) return;
+  const int row_lo = pr0 / G;
+  const int row_hi = (min(n_packed, pr0 + LA_BM) - 1) / G;
+  const int pos0 = sl - nq;
+  const int hi_key = pos0 + row_hi + 1;
+  const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
+  int k_begin = lo_key, k_end = hi_key;
+  if (nsplit > 1) {
+    const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int s0 = lo_req / p.split_keys;
+    k_begin = max(lo_key, (s0 + split) * p.split_keys);
+    k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* q = (const float*)p.q;
+  const T* kc = (const T*)p.k_cache;
+  const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
+
+  for (int idx = threadIdx.x; idx < LA_BM * DK; idx += blockDim.x) {
+    const int i = idx / DK, d = idx - i * DK;
+    const int pr = pr0 + i;
+    float v = 0.f;
+    if (pr < n_packed) {
+      const int row = pr / G, hg = pr - row * G;
+      v = q[((size_t)(qs + row) * H + hg) * DK + d];
+    }
+    Qs[idx] = v;
+  }
+  float m_run[LA_RPW], l_run[LA_RPW], acc[LA_RPW][DPL];
+#pragma unroll
+  for (int j = 0; j < LA_RPW; ++j) {
+    m_run[j] = -INFINITY;
+    l_run[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[j][i] = 0.f;
+  }
+  const int tile0 = (k_begin / LA_BN) * LA_BN;
+  for (int ts = tile0; ts < k_end; ts += LA_BN) {
+    __syncthreads();       // the tile before is consumed (and Qs is written, the first time)
+    // every warp brings eight of the tile's rows, the lanes along a row
+    {
+      const int my_key = ts + lane;
+      int my_page = -1;
+      if (my_key >= k_begin && my_key < k_end) my_page = bt[my_key / P];
+#pragma unroll
+      for (int jj = 0; jj < LA_BN / LA_WARPS; ++jj) {
+        const int j = warp + jj * LA_WARPS;
+        const int key = ts + j;
+        const int page = __shfl_sync(0xffffffffu, my_page, j);
+        float* dst = Ks + j * KS;
+        if (page >= 0) {
+          const T* src = kc + ((size_t)page * P + (key % P)) * DK;
+          for (int d = lane; d < DK; d += 32) dst[d] = to_float(src[d]);
+        } else {
+          for (int d = lane; d < DK; d += 32) dst[d] = 0.f;
+        }
+      }
+    }
+    __syncthreads();
+    float s[LA_RPW];
+#pragma unroll
+    for (int j = 0; j < LA_RPW; ++j) s[j] = 0.f;
+    {
+      const float* krow = Ks + lane * KS;
+      for (int d = 0; d < DK; ++d) {
+        const float kv = krow[d];
+#pragma unroll
+        for (int j = 0; j < LA_RPW; ++j) s[j] = fmaf(Qs[(warp + j * LA_WARPS) * DK + d], kv, s[j]);
+      }
+    }
+    float pj[LA_RPW];
+#pragma unroll
+    for (int j = 0; j < LA_RPW; ++j) {
+      const int pr = pr0 + warp + j * LA_WARPS;
+      pj[j] = 0.f;
+      if (pr >= n_packed) continue;
+      const int pos = pos0 + pr / G;
+      const int key = ts + lane;
+      const int row_lo_key = p.window > 0 ? pos - p.window + 1 : 0;
+      const bool visible = key >= k_begin && key < k_end && key <= pos && key >= row_lo_key;
+      const float sc = visible ? s[j] * p.scale : -INFINITY;
+      const float m_new = fmaxf(m_run[j], warp_max(sc));
+      if (m_new == -INFINITY) continue;
+      pj[j] = visible ? expf(sc - m_new) : 0.f;
+      const float alpha = expf(m_run[j] - m_new);
+      l_run[j] = l_run[j] * alpha + warp_sum(pj[j]);
+      m_run[j] = m_new;
+#pragma unroll
+      for (int ii = 0; ii < DPL; ++ii) acc[j][ii] *= alpha;
+    }
+    for (int kk = 0; kk < LA_BN; ++kk) {
+      float vv[DPL];
+#pragma unroll
+      for (int ii = 0; ii < DPL; ++ii) {
+        const int d = lane + ii * 32;
+        vv[ii] = d < DV ? Ks[kk * KS + d] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < LA_RPW; ++j) {
+        const float pk = __shfl_sync(0xffffffffu, pj[j], kk);
+#pragma unroll
+        for (int ii = 0; ii < DPL; ++ii) acc[j][ii] = fmaf(pk, vv[ii], acc[j][ii]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < LA_RPW; ++j) {
+    const int pr = pr0 + warp + j * LA_WARPS;
+    if (pr >= n_packed) continue;
+    const int row = pr / G, head = pr - row * G;
+    const int t = qs + row;
+    if (nsplit <= 1) {
+      // the sink joins the denominator once: a logit without key or value
+      float m_fin = m_run[j], l = l_run[j], factor = 1.f;
+      if (lp.sink) {
+        const float sk = lp.sink[head];
+        m_fin = fmaxf(m_run[j], sk);
+        factor = expf(m_run[j] - m_fin);
+        l = l * factor + expf(sk - m_fin);
+      }
+      const float inv = l > 0.f ? factor / l : 0.f;
+      float* o = (float*)p.out + ((size_t)t * H + head) * DV;
+#pragma unroll
+      for (int ii = 0; ii < DPL; ++ii) {
+        const int d = lane + ii * 32;
+        if (d < DV) o[d] = acc[j][ii] * inv;
+      }
+    } else {
+      const int srow = p.tok_split_row[t];
+      const size_t base = ((size_t)srow * H + head) * p.max_splits + split;
+      float* po = p.part_o + base * DV;
+#pragma unroll
+      for (int ii = 0; ii < DPL; ++ii) {
+        const int d = lane + ii * 32;
+        if (d < DV) po[d] = acc[j][ii];
+      }
+      if (lane == 0) {
+        p.part_ml[base * 2] = m_run[j];
+        p.part_ml[base * 2 + 1] = l_run[j];
+      }
+    }
+  }
+}
+
+struct LatentMergeParams {
+  AttnMergeParams m;         // out: float32 [T, H, head_dim]
+  const float* sink;
+};
+
+__global__ void latent_merge_kernel(LatentMergeParams lp) {
+  const AttnMergeParams& p = lp.m;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int srow = blockIdx.x, head = blockIdx.y;
+  const int n = p.split_counts[srow];
+  if (n <= 1) return;
+  const int t = p.split_tokens[srow];
+  const size_t base = ((size_t)srow * p.num_heads + head) * p.max_splits;
+  float m = lp.sink ? lp.sink[head] : -INFINITY;
+  for (int s = 0; s < n; ++s) m = fmaxf(m, p.part_ml[(base + s) * 2]);
+  float l = lp.sink ? expf(lp.sink[head] - m) : 0.f;
+  for (int s = 0; s < n; ++s) {
+    const float ms = p.part_ml[(base + s) * 2];
+    if (ms != -INFINITY) l += p.part_ml[(base + s) * 2 + 1] * expf(ms - m);
+  }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  float* o = (float*)p.out + ((size_t)t * p.num_heads + head) * p.head_dim;
+  for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n; ++s) {
+      const float ms = p.part_ml[(base + s) * 2];
+      if (ms != -INFINITY) a += p.part_o[(base + s) * p.head_dim + d] * expf(ms - m);
+    }
+    o[d] = a * inv;
+  }
+}
+
+template <typename T, int DPL>
+int launch_latent(const LatentAttnParams& lp, int num_work, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * ((size_t)LA_BM * lp.dk + (size_t)LA_BN * (lp.dk | 1));
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  static size_t opted = 48 * 1024;
+  if (smem > opted) {
+    cudaFuncSetAttribute(latent_attention_kernel<T, DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    opted = 200 * 1024;
+  }
+  dim3 grid(num_work, lp.a.tile_rows / LA_BM);
+  launch_k(latent_attention_kernel<T, DPL>, grid, LA_WARPS * 32, smem, stream, lp);
+  return launch_status();
+}
+
+template <typename T>
+int dispatch_latent(const LatentAttnParams& lp, int num_work, cudaStream_t stream) {
+  const int dpl = (lp.dv + 31) / 32;
+  if (dpl <= 1) return launch_latent<T, 1>(lp, num_work, stream);
+  if (dpl <= 2) return launch_latent<T, 2>(lp, num_work, stream);
+  if (dpl <= 4) return launch_latent<T, 4>(lp, num_work, stream);
+  if (dpl <= 8) return launch_latent<T, 8>(lp, num_work, stream);
+  if (dpl <= 16) return launch_latent<T, 16>(lp, num_work, stream);
+  return (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+PBE_EXPORT int pbe_latent_prepare(const void* proj, int ld, int dtype, int q_off, int q_rank, int c_off, int rank,
+                                  int r_off, int rot, const float* q_gain, const float* c_gain, const float* inv_freq,
+                                  int rot_dims, const int32_t* positions, const int32_t* slots, void* q_lat, void* cache,
+                                  float eps, int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  PrepareParams p{proj, ld, q_off, q_rank, c_off, rank, r_off, rot, q_gain, c_gain, inv_freq, rot_dims, positions,
+                  slots, q_lat, cache, eps};
+  const int widest = q_rank > rank ? q_rank : rank;
+  const int threads = widest >= 1024 ? 256 : 128;
+  if (dtype == PBE_F32) launch_k(latent_prepare_kernel<float>, T, threads, 0, stream, p);
+  else launch_k(latent_prepare_kernel<__nv_bfloat16>, T, threads, 0, stream, p);
+  return launch_status();
+}
+
+// a_dtype: dtype of a; w_dtype: of the weights and of the gate; out_dtype: of the result
+PBE_EXPORT int pbe_head_product(const void* a, int lda, int ha, int a_dtype, const void* w, long long hw, int wk, int wn,
+                                int w_dtype, void* out, int ldo, int ho, int out_dtype, int T, int H, int K, int N,
+                                int rot, int rot_dims, const float* inv_freq, const int32_t* positions,
+                                const void* gate, int ldg, cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return 0;
+  HeadProductParams p{a, lda, ha, w, hw, wk, wn, out, ldo, ho, T, H, K, N, rot, rot_dims, inv_freq, positions, gate, ldg};
+  dim3 grid((T + HP_TM - 1) / HP_TM, H, (N + HP_TN - 1) / HP_TN);
+  if (grid.z == 0) grid.z = 1;
+  const int code = a_dtype * 4 + w_dtype * 2 + out_dtype;
+  switch (code) {
+    case 0: launch_k(head_product_kernel<float, float, float>, grid, 256, 0, stream, p); break;
+    case 4 + 2 + 0: launch_k(head_product_kernel<__nv_bfloat16, __nv_bfloat16, float>, grid, 256, 0, stream, p); break;
+    case 0 + 2 + 1: launch_k(head_product_kernel<float, __nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, p); break;
+    case 4 + 2 + 1:
+      launch_k(head_product_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, p); break;
+    default: return (int)cudaErrorInvalidValue;
+  }
+  return launch_status();
+}
+
+PBE_EXPORT int pbe_latent_attention(const AttnParams* params, const float* sink, int dk, int dv, int num_work,
+                                    int cache_dtype, cudaStream_t stream) {
+  if (num_work <= 0) return 0;
+  LatentAttnParams lp{*params, sink, dk, dv};
+  if (lp.a.tile_rows % LA_BM != 0 || lp.a.split_keys % LA_BN != 0 || dv > dk) return (int)cudaErrorInvalidValue;
+  return cache_dtype == PBE_F32 ? dispatch_latent<float>(lp, num_work, stream)
+                                : dispatch_latent<__nv_bfloat16>(lp, num_work, stream);
+}
+
+PBE_EXPORT int pbe_latent_merge(const AttnMergeParams* params, const float* sink, int split_rows, cudaStream_t stream) {
+  if (split_rows <= 0) return 0;
+  LatentMergeParams lp{*params, sink};
+  dim3 grid(split_rows, lp.m.num_heads);
+  launch_k(latent_merge_kernel, grid, lp.m.head_dim >= 128 ? 128 : 64, 0, stream, lp);
+  return launch_status();
+}

@@ -1,5 +1,8 @@
-// Linear attention with a fixed decay per head, as a recurrence over a float32 state:
+// Linear attention with a decay per head, as a recurrence over a float32 state:
 //   S_t = lambda_h S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t      (S: [D, E] per head and request)
+// and its selective form, in which the decay and a factor on v differ from token to token, q and
+// k are shared by a group of heads and the output has a skip term:
+//   S_t = a_{t,h} S_{t-1} + k_t (s_{t,h} v_t)^T,   o_t = S_t^T q_t + skip_h v_t
 // q, k (D wide) and v (E wide) are slices of one wider projection matrix; an activation (silu)
 // and a scale on k are applied as they are read, in float32.  The state lives in a row of a
 // per-request table, is read at the start of a request's rows of this step and written back
@@ -45,6 +48,15 @@ struct LinAttnParams {
   int H, D, E;
   float k_scale;
   int act;                  // 1: silu on q, k and v
+  // selective variants (all optional): a decay per token and head instead of the head's constant,
+  // a factor per token and head on v as it enters the state, a term skip_h * v_t added to the
+  // output, and q / k shared by `kq_share` neighbouring heads (a group's q and k lie once in the
+  // projection)
+  const float* tok_decay;   // [T, H] or null
+  const float* tok_scale;   // [T, H] or null
+  const float* skip;        // [H] or null
+  int kq_share;             // heads that share one q and k (1: every head its own)
+  float* chunk_decay;       // [entries, H]: product of a chunk's decays, written by the pass without outputs
 };
 
 // silu with the fast exponential and division (errors of a few units in the last place of float32)
@@ -91,14 +103,16 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
   float S[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) S[i] = (st_in && live && d0 + i < D) ? st_in[(size_t)(d0 + i) * E + e] : 0.f;
-  const float lam = p.decay[h];
-  const T* qp = (const T*)p.q + (size_t)h * D;
-  const T* kp = (const T*)p.k + (size_t)h * D;
+  const float lam = p.decay ? p.decay[h] : 1.f;
+  const float skip = p.skip ? p.skip[h] : 0.f;
+  const T* qp = (const T*)p.q + (size_t)(h / p.kq_share) * D;
+  const T* kp = (const T*)p.k + (size_t)(h / p.kq_share) * D;
   const T* vp = (const T*)p.v + (size_t)h * E;
   constexpr int PER = (DMAX + NT - 1) / NT;    // q and k elements of a token a thread fetches
   // a batch of TB tokens travels together: all its loads are in flight at once, and it waits in
   // registers while the batch before it is computed
   T qn[TB][PER], kn[TB][PER], vn[TB];
+  float dn[TB], sn[TB];        // the tokens' decays and factors on v
   auto fetch = [&](int b) {
 #pragma unroll
     for (int tt = 0; tt < TB; ++tt) {
@@ -112,9 +126,13 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
         kn[tt][i] = (ok && d < D) ? kp[row + d] : from_float<T>(0.f);
       }
       vn[tt] = (ok && live) ? vp[row + e] : from_float<T>(0.f);
+      const size_t th = (size_t)(t0 + (ok ? t : 0)) * H + h;
+      dn[tt] = p.tok_decay ? p.tok_decay[th] : lam;
+      sn[tt] = p.tok_scale ? p.tok_scale[th] : 1.f;
     }
   };
-  float vcur[TB];
+  float vcur[TB], xcur[TB], dcur[TB];
+  float decay_product = 1.f;
   auto stage = [&](int buf) {
 #pragma unroll
     for (int tt = 0; tt < TB; ++tt) {
@@ -127,7 +145,9 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
           ks[buf][tt][at] = act_of(to_float(kn[tt][i]), p.act) * p.k_scale;
         }
       }
-      vcur[tt] = act_of(to_float(vn[tt]), p.act);
+      xcur[tt] = act_of(to_float(vn[tt]), p.act);
+      vcur[tt] = xcur[tt] * sn[tt];
+      dcur[tt] = dn[tt];
     }
   };
   const int nb = (n + TB - 1) / TB;
@@ -145,6 +165,8 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
       const float* kb = ks[b & 1][tt] + part * PSTRIDE;
       const float* qb = qs[b & 1][tt] + part * PSTRIDE;
       const float v = vcur[tt];
+      const float lam = dcur[tt];
+      decay_product *= lam;
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;       // four chains: the sum's latency does not bind
       if (p.out) {
 #pragma unroll
@@ -173,7 +195,7 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
       float o = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int m = 1; m < PARTS; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-      if (p.out && live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = o;
+      if (p.out && live && part == 0) p.out[(size_t)(t0 + t) * H * E + (size_t)h * E + e] = fmaf(skip, xcur[tt], o);
     }
     if (b + 1 < nb) {
       stage((b + 1) & 1);
@@ -185,6 +207,7 @@ __global__ void __launch_bounds__(32 * WARPS) linear_attention_kernel(LinAttnPar
     for (int i = 0; i < DPT; ++i)
       if (d0 + i < D) st[(size_t)(d0 + i) * E + e] = S[i];
   }
+  if (p.chunk_decay && dst <= -2 && tid == 0 && blockIdx.z == 0) p.chunk_decay[(size_t)(-(dst + 2)) * H + h] = decay_product;
 }
 
 // The states at the chunks' starts from the chunks' own contributions, in place (see the top).
@@ -194,6 +217,7 @@ struct ScanParams {
   const float* decay;
   const int32_t* desc;      // [m, 4]: state row, first scratch entry, chunks, rows of every chunk but the last
   int H, D, E;
+  const float* chunk_decay; // [entries, H] or null: the chunks' own decay products (decays that differ by token)
 };
 
 __global__ void chunk_scan_kernel(ScanParams p) {
@@ -204,13 +228,15 @@ __global__ void chunk_scan_kernel(ScanParams p) {
   const size_t per_head = (size_t)p.D * p.E;
   const size_t i = (size_t)blockIdx.z * blockDim.x + threadIdx.x;
   if (i >= per_head) return;
-  const float lam = p.decay[h];
+  const float lam = p.decay ? p.decay[h] : 1.f;
   float lam_n = 1.f;
-  for (int j = 0; j < d[3]; ++j) lam_n *= lam;
+  if (!p.chunk_decay)
+    for (int j = 0; j < d[3]; ++j) lam_n *= lam;
   float S = p.state[((size_t)d[0] * p.H + h) * per_head + i];
   for (int c = 0; c < d[2]; ++c) {
     float* u = p.scratch + ((size_t)(d[1] + c) * p.H + h) * per_head + i;
     const float own = c + 1 < d[2] ? *u : 0.f;
+    if (p.chunk_decay && c + 1 < d[2]) lam_n = p.chunk_decay[(size_t)(d[1] + c) * p.H + h];
     *u = S;
     S = fmaf(lam_n, S, own);
   }
@@ -243,16 +269,19 @@ int dispatch_la(const LinAttnParams& p, int R, cudaStream_t stream) {
 PBE_EXPORT int pbe_linear_attention(const void* q, const void* k, const void* v, int ld, int dtype, float* out,
                                     float* state, const float* decay, const int32_t* q_start, const int32_t* q_len,
                                     const int32_t* slots, const int32_t* items, float* scratch, int R, int H, int D,
-                                    int E, float k_scale, int act, cudaStream_t stream) {
+                                    int E, float k_scale, int act, const float* tok_decay, const float* tok_scale,
+                                    const float* skip, int kq_share, float* chunk_decay, cudaStream_t stream) {
   if (R <= 0) return 0;
-  LinAttnParams p{q, k, v, ld, out, state, decay, q_start, q_len, slots, items, scratch, H, D, E, k_scale, act};
+  if (kq_share < 1 || H % kq_share != 0) return (int)cudaErrorInvalidValue;
+  LinAttnParams p{q, k, v, ld, out, state, decay, q_start, q_len, slots, items, scratch, H, D, E, k_scale, act,
+                  tok_decay, tok_scale, skip, kq_share, chunk_decay};
   return dtype == PBE_F32 ? dispatch_la<float>(p, R, stream) : dispatch_la<__nv_bfloat16>(p, R, stream);
 }
 
 PBE_EXPORT int pbe_linear_attention_scan(float* state, float* scratch, const float* decay, const int32_t* desc,
-                                         int m, int H, int D, int E, cudaStream_t stream) {
+                                         int m, int H, int D, int E, const float* chunk_decay, cudaStream_t stream) {
   if (m <= 0) return 0;
-  ScanParams p{state, scratch, decay, desc, H, D, E};
+  ScanParams p{state, scratch, decay, desc, H, D, E, chunk_decay};
   dim3 grid(m, H, (unsigned)(((size_t)D * E + 255) / 256));
   launch_k(chunk_scan_kernel, grid, 256, 0, stream, p);
   return launch_status();

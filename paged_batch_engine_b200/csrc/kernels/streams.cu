@@ -13,7 +13,8 @@
 // over the row and multiplied by a gain of its own.
 //
 // gated_rms: o / rms(o) (over the whole row or over each head's slice), times an optional
-// gain, times sigmoid(g) or silu(g) of a gate that lies in a wider matrix.
+// gain, times sigmoid(g) or silu(g) of a gate that lies in a wider matrix; or, gate first, the
+// gated values o * act(g) divided by their own root mean square, times the gain.
 #include "common.cuh"
 #include "pdl.cuh"
 
@@ -152,6 +153,7 @@ struct GatedRmsParams {
   float eps;
   int per_head;            // 1: each head's E values have a root mean square of their own
   int gate_act;            // 0: sigmoid, 1: silu
+  int gate_first;          // 1: the gate multiplies o before the root mean square is taken (of the gated values)
 };
 
 template <typename T>
@@ -163,19 +165,24 @@ __global__ void gated_rms_kernel(GatedRmsParams p) {
   const float* o = p.o + (size_t)t * N;
   const T* g = (const T*)p.gate + (size_t)t * p.ld_gate;
   T* out = (T*)p.out + (size_t)t * N;
-  auto finish = [&](int c, float scale) {
+  auto gate_of = [&](int c) {
     const float gv = to_float(g[c]);
     const float sg = 1.0f / (1.0f + expf(-gv));
-    float v = o[c] * scale;
+    return p.gate_act ? gv * sg : sg;
+  };
+  // what the root mean square is taken of: o itself, or (gate_first) o times its gate
+  auto value = [&](int c) { return p.gate_first ? o[c] * gate_of(c) : o[c]; };
+  auto finish = [&](int c, float scale) {
+    float v = value(c) * scale;
     if (p.gain) v *= p.gain[c];
-    out[c] = from_float<T>(v * (p.gate_act ? gv * sg : sg));
+    out[c] = from_float<T>(p.gate_first ? v : v * gate_of(c));
   };
   if (p.per_head) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int h = warp; h < H; h += nw) {
       float ss = 0.f;
       for (int e = lane; e < E; e += 32) {
-        const float v = o[h * E + e];
+        const float v = value(h * E + e);
         ss += v * v;
       }
       const float scale = rsqrtf(warp_sum(ss) / (float)E + p.eps);
@@ -184,7 +191,10 @@ __global__ void gated_rms_kernel(GatedRmsParams p) {
     return;
   }
   float ss = 0.f;
-  for (int c = threadIdx.x; c < N; c += blockDim.x) ss += o[c] * o[c];
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    const float v = value(c);
+    ss += v * v;
+  }
   const float scale = rsqrtf(block_sum(ss, red) / (float)N + p.eps);
   for (int c = threadIdx.x; c < N; c += blockDim.x) finish(c, scale);
 }
@@ -236,9 +246,10 @@ PBE_EXPORT int pbe_branch_rms_mean(const void* const* x, const float* const* gai
 }
 
 PBE_EXPORT int pbe_gated_rms(const float* o, const void* gate, int ld_gate, const float* gain, void* out, int dtype,
-                             int T, int H, int E, float eps, int per_head, int gate_act, cudaStream_t stream) {
+                             int T, int H, int E, float eps, int per_head, int gate_act, int gate_first,
+                             cudaStream_t stream) {
   if (T <= 0) return 0;
-  GatedRmsParams p{o, gate, gain, out, ld_gate, H, E, eps, per_head, gate_act};
+  GatedRmsParams p{o, gate, gain, out, ld_gate, H, E, eps, per_head, gate_act, gate_first};
   const int threads = H * E >= 512 ? 256 : 128;
   if (dtype == PBE_F32) launch_k(gated_rms_kernel<float>, T, threads, 0, stream, p);
   else launch_k(gated_rms_kernel<__nv_bfloat16>, T, threads, 0, stream, p);

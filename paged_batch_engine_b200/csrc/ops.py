@@ -209,10 +209,11 @@ def branch_rms_mean(branches, gains, eps: float) -> torch.Tensor:
 
 
 def gated_rms(o: torch.Tensor, gate: torch.Tensor, gain: Optional[torch.Tensor], heads: int, eps: float,
-              per_head: bool, gate_act: str, out_dtype: torch.dtype) -> torch.Tensor:
+              per_head: bool, gate_act: str, out_dtype: torch.dtype, gate_first: bool = False) -> torch.Tensor:
     """out = o / rms(o) (* gain) * act(gate): ``o`` float32 [T, heads * E]; the root mean square
     over the whole row or over each head's E values; ``gate`` a column slice [T, heads * E] of a
-    wider matrix (unit column stride); ``gate_act`` "sigmoid" or "silu"."""
+    wider matrix (unit column stride); ``gate_act`` "sigmoid" or "silu".  ``gate_first``: out =
+    u / rms(u) (* gain) with u = o * act(gate), the gate inside the norm."""
     _need_cuda(o, gate, gain)
     _need_contiguous(o, gain)
     T, N = o.shape
@@ -226,9 +227,10 @@ def gated_rms(o: torch.Tensor, gate: torch.Tensor, gain: Optional[torch.Tensor],
         raise KernelError(f"gated_rms: unknown gate activation {gate_act!r}")
     out = torch.empty((T, N), dtype=out_dtype, device=o.device)
     fn = _fn("streams", "pbe_gated_rms", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                          c_float, c_int, c_int, c_void_p])
+                                          c_float, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(o), _ptr(gate), gate.stride(0) if T > 1 else N, _ptr(gain), _ptr(out), _dtype_code(out), T, heads,
-              N // heads, float(eps), 1 if per_head else 0, 1 if gate_act == "silu" else 0, _stream()), "gated_rms")
+              N // heads, float(eps), 1 if per_head else 0, 1 if gate_act == "silu" else 0, 1 if gate_first else 0,
+              _stream()), "gated_rms")
     return out
 
 
@@ -240,14 +242,21 @@ def _column_slice(x: torch.Tensor, what: str):
 
 def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
                      q_start: torch.Tensor, q_len: torch.Tensor, slots: torch.Tensor, num_requests: int,
-                     heads: int, k_scale: float = 1.0, silu: bool = False, plan=None) -> torch.Tensor:
+                     heads: int, k_scale: float = 1.0, silu: bool = False, plan=None,
+                     tok_decay: Optional[torch.Tensor] = None, tok_scale: Optional[torch.Tensor] = None,
+                     skip: Optional[torch.Tensor] = None, kq_share: int = 1) -> torch.Tensor:
     """o_t = S_t^T q_t with S_t = decay_h S_{t-1} + k_t v_t^T per head, request by request over
     the rows each brings (``q_start``, ``q_len`` int32 [R]); ``state`` float32 [slots, H, D, E]
     is read at ``slots[r]`` and left updated.  q, k [T, H*D] and v [T, H*E] are column slices of
     one projection matrix (equal row stride).  ``plan`` (a ``RecurrencePlan`` of the step): long
     portions are cut into chunks that run side by side, their start states made by a scan over
-    the chunks' own contributions.  Returns float32 [T, H*E]."""
-    _need_cuda(q, k, v, state, decay, q_start, q_len, slots)
+    the chunks' own contributions.  The selective form: ``tok_decay`` float32 [T, H] replaces the
+    heads' constant decays (``decay`` may then be None), ``tok_scale`` float32 [T, H] multiplies v
+    as it enters the state, ``skip`` float32 [H] adds skip_h v_t to the output, and ``kq_share``
+    neighbouring heads read one q and k (q, k are then [T, H / kq_share * D]).
+    Returns float32 [T, H*E]."""
+    _need_cuda(q, k, v, state, decay, q_start, q_len, slots, tok_decay, tok_scale, skip)
+    _need_contiguous(tok_decay, tok_scale, skip)
     for x in (q, k, v):
         _column_slice(x, "linear_attention")
     T = q.shape[0]
@@ -256,12 +265,21 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: t
         raise KernelError("linear_attention: q, k and v must share a row stride")
     if q.dtype != k.dtype or q.dtype != v.dtype:
         raise KernelError("linear_attention: q, k and v share a dtype")
-    D, E = q.shape[1] // heads, v.shape[1] // heads
-    if q.shape[1] != heads * D or k.shape[1] != heads * D or v.shape[1] != heads * E:
+    if kq_share < 1 or heads % kq_share:
+        raise KernelError("linear_attention: kq_share must divide the head count")
+    kq_heads = heads // kq_share
+    D, E = q.shape[1] // kq_heads, v.shape[1] // heads
+    if q.shape[1] != kq_heads * D or k.shape[1] != kq_heads * D or v.shape[1] != heads * E:
         raise KernelError("linear_attention: widths are not multiples of the head count")
+    for name, x, shape in (("tok_decay", tok_decay, (T, heads)), ("tok_scale", tok_scale, (T, heads)),
+                           ("skip", skip, (heads,))):
+        if x is not None and (x.dtype != torch.float32 or tuple(x.shape) != shape):
+            raise KernelError(f"linear_attention: {name} must be float32 {list(shape)}")
+    if decay is None and tok_decay is None:
+        raise KernelError("linear_attention: give the heads' decays or the tokens'")
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, D, E) or not state.is_contiguous():
         raise KernelError("linear_attention: the state is float32 [slots, heads, D, E]")
-    if decay.dtype != torch.float32 or decay.numel() != heads:
+    if decay is not None and (decay.dtype != torch.float32 or decay.numel() != heads):
         raise KernelError("linear_attention: decay is float32 [heads]")
     for x in (q_start, q_len, slots):
         if x.dtype != torch.int32 or x.numel() < num_requests:
@@ -271,21 +289,26 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: t
     out = torch.empty((T, heads * E), dtype=torch.float32, device=q.device)
     fn = _fn("linear_attention", "pbe_linear_attention",
              [c_void_p, c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int,
-                                                                             c_void_p])
+                                                                             c_void_p, c_void_p, c_void_p, c_int,
+                                                                             c_void_p, c_void_p])
+    chunk_decay = None
 
     def launch(result, items, scratch, n):
         _check(fn(_ptr(q), _ptr(k), _ptr(v), ld, _dtype_code(q), _ptr(result), _ptr(state), _ptr(decay), _ptr(q_start),
                   _ptr(q_len), _ptr(slots), _ptr(items), _ptr(scratch), n, heads, D, E, float(k_scale),
-                  1 if silu else 0, _stream()), "linear_attention")
+                  1 if silu else 0, _ptr(tok_decay), _ptr(tok_scale), _ptr(skip), int(kq_share), _ptr(chunk_decay),
+                  _stream()), "linear_attention")
     if plan is None or plan.num_chunks == 0:
         launch(out, None, None, num_requests)
         return out
     scratch = torch.empty((plan.num_chunks, heads, D, E), dtype=torch.float32, device=q.device)
+    if tok_decay is not None:       # the chunks' decay products, left by the pass that makes their contributions
+        chunk_decay = torch.empty((plan.num_chunks, heads), dtype=torch.float32, device=q.device)
     launch(None, plan.first_pass, scratch, plan.num_first_pass)          # the chunks' own contributions
     scan = _fn("linear_attention", "pbe_linear_attention_scan",
-               [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(scan(_ptr(state), _ptr(scratch), _ptr(decay), _ptr(plan.scan), plan.num_scan, heads, D, E, _stream()),
-           "linear_attention_scan")
+               [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(scan(_ptr(state), _ptr(scratch), _ptr(decay), _ptr(plan.scan), plan.num_scan, heads, D, E,
+                _ptr(chunk_decay), _stream()), "linear_attention_scan")
     launch(out, plan.second_pass, scratch, plan.num_second_pass)         # every chunk from its start state
     return out
 
@@ -1097,3 +1120,315 @@ def apply_penalty(logits, rows, tokens, penalties):
     _check(fn(_ptr(logits), logits.stride(0), logits.shape[1], _ptr(rows), _ptr(tokens),
               _ptr(penalties), n, _stream()), "apply_penalty")
     return logits
+
+
+# ------------------------------------------------------------------ two branches on one residual
+def add2_rmsnorm2(residual: torch.Tensor, delta_a: Optional[torch.Tensor], delta_b: Optional[torch.Tensor],
+                  gain1: torch.Tensor, gain2: Optional[torch.Tensor], eps: float,
+                  out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
+    """residual += (delta_a + delta_b) (float32, in place; either may be None), then the two RMS
+    norms of the same row, out_i = gain_i * x * rsqrt(mean(x^2) + eps).  ``gain2`` None: one norm.
+    With ``rows`` (int32 [n]) output row i is made from batch row rows[i] and the residual is left
+    alone.  Returns (out1, out2 or None)."""
+    _need_cuda(residual, delta_a, delta_b, gain1, gain2, rows)
+    _need_contiguous(residual, delta_a, delta_b, gain1, gain2, rows)
+    d = residual.shape[-1]
+    if residual.dtype != torch.float32 or residual.dim() != 2:
+        raise KernelError("add2_rmsnorm2: the residual stream is float32 [T, W]")
+    for g in (gain1, gain2):
+        if g is not None and (g.dtype != torch.float32 or g.numel() != d):
+            raise KernelError("add2_rmsnorm2: gains are float32 [W]")
+    deltas = [x for x in (delta_a, delta_b) if x is not None]
+    for x in deltas:
+        if x.shape != residual.shape or x.dtype != deltas[0].dtype:
+            raise KernelError("add2_rmsnorm2: the deltas have the residual's shape and one dtype")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("add2_rmsnorm2: rows must be int32")
+    if d * 4 > 200 * 1024:
+        raise KernelError(f"add2_rmsnorm2: a row of {d} floats does not fit in shared memory")
+    n = residual.shape[0] if rows is None else rows.numel()
+    out1 = torch.empty((n, d), dtype=out_dtype, device=residual.device)
+    out2 = torch.empty((n, d), dtype=out_dtype, device=residual.device) if gain2 is not None else None
+    fn = _fn("elementwise", "pbe_add2_rmsnorm2",
+             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+              c_float, c_void_p])
+    _check(fn(_ptr(residual), _ptr(delta_a), _ptr(delta_b), _dtype_code(deltas[0]) if deltas else F32, _ptr(gain1),
+              _ptr(gain2), _ptr(out1), _ptr(out2), _dtype_code(out1), _ptr(rows), n, d, float(eps), _stream()),
+           "add2_rmsnorm2")
+    return out1, out2
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """relu(x)^2 element by element (float32 arithmetic, rounded once)."""
+    _need_cuda(x)
+    _need_contiguous(x)
+    out = torch.empty_like(x)
+    fn = _fn("elementwise", "pbe_relu_squared", [c_void_p, c_void_p, c_int, c_ll, c_void_p])
+    _check(fn(_ptr(x), _ptr(out), _dtype_code(x), x.numel(), _stream()), "relu_squared")
+    return out
+
+
+def scale_softcap(logits: torch.Tensor, scale: float, cap: Optional[float]) -> torch.Tensor:
+    """logits <- logits * scale, then (with a cap) cap * tanh(logits / cap); float32, in place."""
+    _need_cuda(logits)
+    _need_contiguous(logits)
+    if logits.dtype != torch.float32:
+        raise KernelError("scale_softcap: logits are float32")
+    fn = _fn("elementwise", "pbe_scale_softcap", [c_void_p, c_ll, c_float, c_float, c_void_p])
+    _check(fn(_ptr(logits), logits.numel(), float(scale), float(cap or 0.0), _stream()), "scale_softcap")
+    return logits
+
+
+# ------------------------------------------------------------------ short convolution, step sizes
+def short_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+               request_of_row: torch.Tensor, q_start: torch.Tensor, q_len: torch.Tensor, slots: torch.Tensor,
+               num_requests: int, silu: bool = True, update_state: bool = True) -> torch.Tensor:
+    """Causal convolution per channel over each request's rows: ``u`` [T, C] a column slice of a
+    projection, ``weight`` float32 [C, taps] (last column: the current token), ``state`` float32
+    [slots, taps - 1, C] holding each request's last inputs (read, then moved on).  Returns
+    [T, C] in u's dtype."""
+    _need_cuda(u, weight, bias, state, request_of_row, q_start, q_len, slots)
+    _need_contiguous(weight, bias, state)
+    _column_slice(u, "short_conv")
+    T, C = u.shape
+    taps = weight.shape[1]
+    if weight.dtype != torch.float32 or weight.shape[0] != C or (bias is not None and (bias.dtype != torch.float32
+                                                                                     or bias.numel() != C)):
+        raise KernelError("short_conv: weight is float32 [C, taps], bias float32 [C]")
+    if taps > 16:
+        raise KernelError(f"short_conv: at most 16 taps, got {taps}")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps - 1, C):
+        raise KernelError("short_conv: the state is float32 [slots, taps - 1, C]")
+    for x in (request_of_row, q_start, q_len, slots):
+        if x.dtype != torch.int32:
+            raise KernelError("short_conv: the step's arrays are int32")
+    out = torch.empty((T, C), dtype=u.dtype, device=u.device)
+    ld = u.stride(0) if T > 1 else max(u.stride(0), C)
+    fn = _fn("short_conv", "pbe_short_conv",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    global _launches
+    _check(fn(_ptr(u), ld, _dtype_code(u), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(request_of_row),
+              _ptr(q_start), _ptr(q_len), _ptr(slots), T, int(num_requests), C, taps, 1 if silu else 0,
+              1 if update_state else 0, _stream()), "short_conv")
+    if update_state and taps > 1:
+        _launches += 1
+    return out
+
+
+def step_sizes(u: torch.Tensor, bias: torch.Tensor, rate_log: torch.Tensor):
+    """(dt, decay), float32 [T, H]: dt = softplus(u + bias_h), decay = exp(-exp(rate_log_h) * dt);
+    ``u`` [T, H] is a column slice of a projection."""
+    _need_cuda(u, bias, rate_log)
+    _column_slice(u, "step_sizes")
+    T, H = u.shape
+    if bias.dtype != torch.float32 or rate_log.dtype != torch.float32 or bias.numel() != H or rate_log.numel() != H:
+        raise KernelError("step_sizes: bias and rate_log are float32 [H]")
+    dt = torch.empty((T, H), dtype=torch.float32, device=u.device)
+    decay = torch.empty((T, H), dtype=torch.float32, device=u.device)
+    ld = u.stride(0) if T > 1 else max(u.stride(0), H)
+    fn = _fn("short_conv", "pbe_step_sizes", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_int, c_void_p])
+    _check(fn(_ptr(u), ld, _dtype_code(u), _ptr(bias), _ptr(rate_log), _ptr(dt), _ptr(decay), T, H, _stream()),
+           "step_sizes")
+    return dt, decay
+
+
+# ------------------------------------------------------------------ attention over a compressed latent
+LATENT_TILE = 16     # packed rows (row x head) a block of the latent attention kernel takes
+
+
+def latent_tile_rows(num_heads: int) -> int:
+    """Packed rows of a row tile of the work list: all heads of a row lie in one tile."""
+    return LATENT_TILE * ((num_heads + LATENT_TILE - 1) // LATENT_TILE)
+
+
+def latent_prepare(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, rank: int, r_off: int, rot: int,
+                   q_gain: Optional[torch.Tensor], c_gain: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                   rot_dims: int, positions: torch.Tensor, slots: Optional[torch.Tensor],
+                   cache: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
+    """From the fused down projection [T, ld]: the RMS-normed query latent (returned, [T, q_rank];
+    None when q_rank is 0) and, written into ``cache`` ([page, 1, page_tokens, rank + rot]) at
+    ``slots``: the RMS-normed latent c followed by the rotated shared key part."""
+    _need_cuda(proj, q_gain, c_gain, inv_freq, positions, slots, cache)
+    _need_contiguous(proj, q_gain, c_gain, inv_freq, positions, slots, cache)
+    T = proj.shape[0]
+    if cache is not None and (cache.dtype != proj.dtype or cache.shape[-1] != rank + rot or cache.shape[1] != 1):
+        raise KernelError("latent_prepare: cache pages are [page, 1, page_tokens, rank + rot] in the activations' dtype")
+    if c_gain.dtype != torch.float32 or c_gain.numel() != rank or (q_rank and (q_gain.dtype != torch.float32
+                                                                              or q_gain.numel() != q_rank)):
+        raise KernelError("latent_prepare: gains are float32 of the latents' widths")
+    if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise KernelError("latent_prepare: inv_freq is float32 [rot_dims / 2]")
+    if rot_dims > rot or rot % 2 or rot_dims % 2:
+        raise KernelError("latent_prepare: the rotated part is even and at least rot_dims wide")
+    q_lat = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device) if q_rank else None
+    fn = _fn("latent_attention", "pbe_latent_prepare",
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), _dtype_code(proj), q_off, q_rank, c_off, rank, r_off, rot, _ptr(q_gain),
+              _ptr(c_gain), _ptr(inv_freq), int(rot_dims), _ptr(positions), _ptr(slots), _ptr(q_lat), _ptr(cache),
+              float(eps), T, _stream()), "latent_prepare")
+    return q_lat
+
+
+def head_product(a: torch.Tensor, lda: int, head_stride: int, K: int, w: torch.Tensor, w_head_stride: int,
+                 wk: int, wn: int, N: int, out: torch.Tensor, ldo: int, out_head_stride: int, T: int, H: int,
+                 rot: int = 0, rot_dims: int = 0, inv_freq: Optional[torch.Tensor] = None,
+                 positions: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, h, n] = sum_k a[t, h, k] * w[h][k * wk + n * wn] for n < N, per head, float32 sums in
+    k order.  ``rot`` > 0: out[t, h, N : N + rot] = the rotation of a[t, h, K : K + rot] by the rows'
+    positions (pairs (2i, 2i + 1) of its first ``rot_dims`` values).  ``gate`` [T, >= H] (a column
+    slice in the weights' dtype): the result is multiplied by sigmoid(gate[t, h])."""
+    _need_cuda(a, w, out, inv_freq, positions, gate)
+    if gate is not None and (gate.stride(1) != 1 or gate.dtype != w.dtype):
+        raise KernelError("head_product: the gate is a column slice in the weights' dtype")
+    fn = _fn("latent_attention", "pbe_head_product",
+             [c_void_p, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    ldg = 0
+    if gate is not None:
+        ldg = gate.stride(0) if T > 1 else max(gate.stride(0), H)
+    _check(fn(_ptr(a), int(lda), int(head_stride), _dtype_code(a), _ptr(w), int(w_head_stride), int(wk), int(wn),
+              _dtype_code(w), _ptr(out), int(ldo), int(out_head_stride), _dtype_code(out), int(T), int(H), int(K),
+              int(N), int(rot), int(rot_dims), _ptr(inv_freq), _ptr(positions), _ptr(gate), int(ldg), _stream()),
+           "head_product")
+    return out
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, sink: Optional[torch.Tensor], meta, num_heads: int,
+                     value_width: int, scale: float, window, page_tokens: int) -> torch.Tensor:
+    """Causal attention of every row over its request's cached rows, all heads sharing them:
+    ``q`` float32 [T, H, dk], ``cache`` [page, 1, page_tokens, dk] whose first ``value_width``
+    values of a row are the value; ``sink`` float32 [H] joins each head's softmax denominator.
+    ``meta``: the step's work list for (group, H heads a group, ``latent_tile_rows(H)``, window).
+    Returns float32 [T, H, value_width]."""
+    _need_cuda(q, cache, sink)
+    _need_contiguous(q, cache, sink)
+    T, H, dk = q.shape
+    if q.dtype != torch.float32 or H != num_heads or cache.shape[-1] != dk or cache.shape[1] != 1:
+        raise KernelError("latent_attention: q is float32 [T, H, dk], the cache [page, 1, page_tokens, dk]")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != H):
+        raise KernelError("latent_attention: the sink is float32 [H]")
+    if value_width > 512 or value_width > dk:
+        raise KernelError("latent_attention: the value is at most 512 wide and a prefix of the cached row")
+    if (dk * 16 + (dk | 1) * 32) * 4 > 200 * 1024:
+        raise KernelError(f"latent_attention: cached rows of {dk} values do not fit in shared memory")
+    out = torch.empty((T, H, value_width), dtype=torch.float32, device=q.device)
+    part_o = part_ml = None
+    if meta.num_split_rows:
+        part_o, part_ml = meta.part_o, meta.part_ml       # the step's buffers, when they have this shape
+        if part_o is None or tuple(part_o.shape) != (meta.num_split_rows, H, meta.max_splits, value_width):
+            part_o = torch.empty((meta.num_split_rows, H, meta.max_splits, value_width), dtype=torch.float32,
+                                 device=q.device)
+            part_ml = torch.empty((meta.num_split_rows, H, meta.max_splits, 2), dtype=torch.float32, device=q.device)
+    p = AttnParams(
+        q=q.data_ptr(), k_cache=cache.data_ptr(), v_cache=cache.data_ptr(), out=out.data_ptr(),
+        part_o=part_o.data_ptr() if part_o is not None else None,
+        part_ml=part_ml.data_ptr() if part_ml is not None else None,
+        q_start=meta.q_start.data_ptr(), q_len=meta.q_len.data_ptr(), seq_len=meta.seq_len.data_ptr(),
+        block_table=meta.block_table.data_ptr(), work=meta.work.data_ptr(),
+        tok_split_row=meta.tok_split_row.data_ptr(), bt_stride=int(meta.bt_stride),
+        num_heads=int(H), num_kv_heads=1, page_tokens=int(page_tokens),
+        window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
+        tile_rows=int(meta.tile_rows), scale=float(scale), kinds=0, num_pages=int(cache.shape[0]))
+    fn = _fn("latent_attention", "pbe_latent_attention",
+             [ctypes.POINTER(AttnParams), c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(ctypes.byref(p), _ptr(sink), dk, int(value_width), int(meta.num_work), _dtype_code(cache), _stream()),
+           "latent_attention")
+    if meta.num_split_rows > 0:
+        mp = AttnMergeParams(part_o=part_o.data_ptr(), part_ml=part_ml.data_ptr(), out=out.data_ptr(),
+                             split_tokens=meta.split_tokens.data_ptr(), split_counts=meta.split_counts.data_ptr(),
+                             num_heads=int(H), head_dim=int(value_width), max_splits=int(meta.max_splits))
+        mfn = _fn("latent_attention", "pbe_latent_merge", [ctypes.POINTER(AttnMergeParams), c_void_p, c_int, c_void_p])
+        _check(mfn(ctypes.byref(mp), _ptr(sink), int(meta.num_split_rows), _stream()), "latent_merge")
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+def route(logits: torch.Tensor, top: int, groups: int, keep: int, scale: float):
+    """(chosen int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E]: softmax
+    scores, experts outside the ``keep`` best of ``groups`` neighbouring groups barred, the top
+    scores chosen, weights = score / (sum of the chosen + 1e-20) * scale."""
+    _need_cuda(logits)
+    _need_contiguous(logits)
+    T, E = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("route: router logits are float32")
+    if E > 512 or top > 32 or groups > 64:
+        raise KernelError("route: at most 512 experts, 32 chosen and 64 groups")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    fn = _fn("routed_experts", "pbe_route", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                            c_void_p])
+    _check(fn(_ptr(logits), _ptr(chosen), _ptr(weights), T, E, int(top), int(groups), int(keep), float(scale),
+              _stream()), "route")
+    return chosen, weights
+
+
+def expert_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                chosen: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t)), e = chosen[t, k]:
+    a block per (row, chosen expert) streams that expert's matrices; for few rows.  ``w_gate_up``
+    [E, 2F, W]: an expert's gate rows followed by its up rows; ``w_down`` [E, W, F]."""
+    _need_cuda(x, w_gate_up, w_down, chosen, weights)
+    _need_contiguous(x, w_gate_up, w_down, chosen, weights)
+    T, W = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    top = chosen.shape[1]
+    if F2 % 2 or tuple(w_down.shape) != (E, W, F) or w_gate_up.shape[2] != W:
+        raise KernelError("expert_rows: gate/up is [E, 2F, W], down is [E, W, F]")
+    if not (x.dtype == w_gate_up.dtype == w_down.dtype):
+        raise KernelError("expert_rows: rows and expert matrices share a dtype")
+    if (W + F) * 4 > 200 * 1024:
+        raise KernelError("expert_rows: a row and an expert's hidden units do not fit in shared memory")
+    part = torch.empty((T, top, W), dtype=torch.float32, device=x.device)
+    out = torch.empty((T, W), dtype=x.dtype, device=x.device)
+    fn = _fn("routed_experts", "pbe_expert_rows", [c_void_p] * 3 + [c_ll] + [c_void_p] * 5 + [c_int] * 5 + [c_void_p])
+    global _launches
+    up = c_void_p(w_gate_up.data_ptr() + F * W * w_gate_up.element_size())
+    _check(fn(_ptr(x), _ptr(w_gate_up), up, 2 * F * W, _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(part),
+              _ptr(out), _dtype_code(x), T, W, F, top, _stream()), "expert_rows")
+    _launches += 1
+    return out
+
+
+def expert_places(chosen: torch.Tensor, num_experts: int):
+    """(counts int32 [E], place int32 [T * top]): how many (row, k) pairs chose each expert, and each
+    pair's place inside its expert's run, in pair order."""
+    _need_cuda(chosen)
+    _need_contiguous(chosen)
+    pairs = chosen.numel()
+    counts = torch.empty(num_experts, dtype=torch.int32, device=chosen.device)
+    place = torch.empty(pairs, dtype=torch.int32, device=chosen.device)
+    fn = _fn("routed_experts", "pbe_expert_places", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(chosen), pairs, int(num_experts), _ptr(counts), _ptr(place), _stream()), "expert_places")
+    return counts, place
+
+
+def expert_gather(x: torch.Tensor, chosen: torch.Tensor, place: torch.Tensor, start: torch.Tensor) -> torch.Tensor:
+    """The rows of x once per chosen expert, sorted by expert: row start[e] + place[pair] = x[t]."""
+    _need_cuda(x, chosen, place, start)
+    _need_contiguous(x, chosen, place, start)
+    T, W = x.shape
+    top = chosen.shape[1]
+    out = torch.empty((T * top, W), dtype=x.dtype, device=x.device)
+    fn = _fn("routed_experts", "pbe_expert_gather", [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
+    _check(fn(_ptr(x), _ptr(chosen), _ptr(place), _ptr(start), _ptr(out), _dtype_code(x), T, top, W, _stream()),
+           "expert_gather")
+    return out
+
+
+def expert_scatter(y: torch.Tensor, chosen: torch.Tensor, place: torch.Tensor, start: torch.Tensor,
+                   weights: torch.Tensor, T: int) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * y[start[e] + place[(t, k)]], e = chosen[t, k], in k order."""
+    _need_cuda(y, chosen, place, start, weights)
+    _need_contiguous(y, chosen, place, start, weights)
+    W = y.shape[1]
+    top = chosen.shape[1]
+    out = torch.empty((T, W), dtype=y.dtype, device=y.device)
+    fn = _fn("routed_experts", "pbe_expert_scatter", [c_void_p] * 6 + [c_int] * 4 + [c_void_p])
+    _check(fn(_ptr(y), _ptr(chosen), _ptr(place), _ptr(start), _ptr(weights), _ptr(out), _dtype_code(y), T, top, W,
+              _stream()), "expert_scatter")
+    return out

@@ -159,4 +159,7 @@ class DecoderModel:
         if ctx.num_wanted == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.add_norm(residual, delta, rows=ctx.want_rows)
-        return ops.linear(h, self.lm_head, None, out_dtype=torch.float32)
+        logits = ops.linear(h, self.lm_head, None, out_dtype=torch.float32)
+        if s.logit_scale != 1.0 or s.logit_softcap:
+            ops.scale_softcap(logits, s.logit_scale, s.logit_softcap)
+        return logits

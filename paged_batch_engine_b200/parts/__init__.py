@@ -1,17 +1,21 @@
 from .base import (Block, CacheTensor, CompositeNeed, FeedForward, KVNeed, Mixer, Norm, PagedNeed, Part, PositionEncoding, StateNeed,
                    build_block, build_part, register_part)
-from .norm import LayerNorm, PendingUpdate, RMSNorm
+from .norm import DeltaSum, LayerNorm, PendingUpdate, RMSNorm
 from .rope import NoPositionEncoding, RotaryEncoding
 from .attention import GQAttention
-from .mlp import SwiGLU
-from .block import PreNormBlock
+from .mlp import ActivationMLP, SwiGLU
+from .routed_experts import RoutedExperts
+from .block import ParallelBlock, PreNormBlock
 from .linear_attention import DecayLinearAttention
 from .pooled_attention import PooledWindowAttention
 from .parallel import ParallelMixer
+from .state_space import SelectiveStateSpace
+from .latent_attention import LatentAttention
 from .streams import StreamBlock, StreamConnection
 
 __all__ = ["Block", "CacheTensor", "CompositeNeed", "FeedForward", "KVNeed", "Mixer", "Norm", "PagedNeed", "Part", "PositionEncoding",
            "StateNeed",
            "build_block", "build_part", "register_part", "RMSNorm", "NoPositionEncoding", "RotaryEncoding",
            "GQAttention", "SwiGLU", "PreNormBlock", "LayerNorm", "PendingUpdate", "DecayLinearAttention",
-           "PooledWindowAttention", "ParallelMixer", "StreamBlock", "StreamConnection"]
+           "PooledWindowAttention", "ParallelMixer", "StreamBlock", "StreamConnection", "DeltaSum", "ActivationMLP",
+           "RoutedExperts", "ParallelBlock", "SelectiveStateSpace", "LatentAttention"]

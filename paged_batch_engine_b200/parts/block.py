@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from ..config.specs import BlockSpec
 from .base import Block, build_part, register_part
+from .norm import DeltaSum
 
 
 class PreNormBlock(Block):
@@ -51,5 +52,44 @@ class PreNormBlock(Block):
         return residual, m
 
 
+class ParallelBlock(PreNormBlock):
+    """x -> x + mixer(norm1(x)) + feed_forward(norm2(x)): both branches read norms of the same
+    residual, which differ in their gains only (one launch makes both), and their outputs travel
+    together as a ``DeltaSum`` into the next layer's norms, where x + (a + b) is formed in
+    float32.  A layer without feed-forward has the mixer branch alone."""
+
+    def __init__(self, spec: BlockSpec, dtype, device):
+        self.spec = spec
+        self.prefix = spec.prefix
+        n = spec.names
+        self.p_mixer = self.prefix + n.get("mixer", "mixer.")
+        self.p_ffn = self.prefix + n.get("feed_forward", "feed_forward.")
+        self.p_norm1 = self.prefix + n.get("norm_mixer", "norm_mixer.")
+        self.p_norm2 = self.prefix + n.get("norm_feed_forward", "norm_feed_forward.")
+        self.norm1 = build_part("norm", spec.norm_mixer, dtype, device)
+        self.mixer = build_part("mixer", spec.mixer, dtype, device)
+        self.norm2 = self.ffn = None
+        if spec.feed_forward is not None:
+            self.norm2 = build_part("norm", spec.norm_feed_forward, dtype, device)
+            self.ffn = build_part("feed_forward", spec.feed_forward, dtype, device)
+        if not hasattr(self.norm1, "add_norm_pair"):
+            raise TypeError("a parallel block needs norms that can be taken in pairs (RMSNorm)")
+
+    def parts(self):
+        out = [(self.norm1, self.p_norm1), (self.mixer, self.p_mixer)]
+        if self.ffn is not None:
+            out += [(self.norm2, self.p_norm2), (self.ffn, self.p_ffn)]
+        return out
+
+    def forward(self, residual, delta, ctx, cache):
+        if self.ffn is None:
+            return residual, self.mixer.forward(self.norm1.add_norm(residual, delta), ctx, cache)
+        h1, h2 = self.norm1.add_norm_pair(self.norm2, residual, delta)
+        a = self.mixer.forward(h1, ctx, cache)
+        return residual, DeltaSum(a, self.ffn.forward(h2, ctx))
+
+
 register_part("block", "prenorm", lambda spec, dtype, device: PreNormBlock(spec, dtype, device),
+              replace=True)
+register_part("block", "parallel", lambda spec, dtype, device: ParallelBlock(spec, dtype, device),
               replace=True)

@@ -63,4 +63,42 @@ class SwiGLU(FeedForward):
         return ops.linear(act, self.w_down, None, out_dtype=self.dtype, kind=8)
 
 
+class ActivationMLP(FeedForward):
+    """m = W_down act(W_up x), no gate and no biases; ``activation`` "relu2": relu(z)^2.
+    Checkpoint tensors: up [inter, hidden], down [hidden, inter] under ``tensor_names`` +
+    ``weight_suffix``."""
+    TENSOR_NAMES = dict(up="up_proj", down="down_proj")
+    ACTIVATIONS = ("relu2",)
+
+    def __init__(self, hidden_size: int, intermediate_size: int, dtype, device, activation: str = "relu2",
+                 tensor_names=None, weight_suffix: str = ".weight"):
+        unknown = set(tensor_names or {}) - set(self.TENSOR_NAMES)
+        if unknown:
+            raise ValueError(f"tensor_names knows up and down; got {sorted(unknown)}")
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {', '.join(self.ACTIVATIONS)}")
+        self.names = dict(self.TENSOR_NAMES, **(tensor_names or {}))
+        self.suffix, self.activation = weight_suffix, activation
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.dtype, self.device = dtype, device
+        self.w_up = self.w_down = None
+
+    def kernel_libraries(self, dtype):
+        return [("elementwise", None)] + ops.gemm_libraries(dtype, self.intermediate_size * self.hidden_size)
+
+    def param_specs(self, prefix):
+        i, h, n = self.intermediate_size, self.hidden_size, self.names
+        return [ParamSpec(prefix + n["up"] + self.suffix, (i, h)), ParamSpec(prefix + n["down"] + self.suffix, (h, i))]
+
+    def load(self, tensors, prefix):
+        n = self.names
+        self.w_up = tensors.pop(prefix + n["up"] + self.suffix).contiguous()
+        self.w_down = tensors.pop(prefix + n["down"] + self.suffix).contiguous()
+
+    def forward(self, x, ctx):
+        z = ops.linear(x, self.w_up, None, out_dtype=self.dtype, kind=32)
+        return ops.linear(ops.relu_squared(z), self.w_down, None, out_dtype=self.dtype, kind=8)
+
+
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "activation_mlp", ActivationMLP, replace=True)

@@ -29,9 +29,20 @@ class RMSNorm(Norm):
         self.gain = tensors[prefix + self.weight_name].to(torch.float32).contiguous()
 
     def add_norm(self, residual, delta, rows=None, out_dtype=None):
+        if isinstance(delta, DeltaSum):
+            return ops.add2_rmsnorm2(residual, delta.a, delta.b, self.gain, None, self.eps,
+                                     out_dtype or self.dtype, rows)[0]
         n = residual.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype or self.dtype, device=residual.device)
         return ops.add_rmsnorm(residual, delta, self.gain, out, self.eps, rows)
+
+    def add_norm_pair(self, other: "RMSNorm", residual, delta, out_dtype=None):
+        """This norm and ``other`` of the same summed row (residual += delta first): the two differ
+        in their gains only, so one launch and one root mean square serve both."""
+        if other.size != self.size or other.eps != self.eps:
+            raise ValueError("two norms of one row share its width and eps")
+        a, b = (delta.a, delta.b) if isinstance(delta, DeltaSum) else (delta, None)
+        return ops.add2_rmsnorm2(residual, a, b, self.gain, other.gain, self.eps, out_dtype or self.dtype)
 
 
 class LayerNorm(Norm):
@@ -94,6 +105,15 @@ class LayerNorm(Norm):
 
     def kernel_libraries(self, dtype):
         return [("streams", None)]
+
+
+class DeltaSum:
+    """Two branch outputs of one layer that are not yet added to the residual: x' = x + (a + b).
+    The next norm's launch adds them."""
+    __slots__ = ("a", "b")
+
+    def __init__(self, a, b):
+        self.a, self.b = a, b
 
 
 class PendingUpdate:

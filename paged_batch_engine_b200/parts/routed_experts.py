@@ -1,0 +1,93 @@
+"""A feed-forward of many small gated experts, of which a router picks a few per token."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import ParamSpec
+from .base import FeedForward, register_part
+
+
+class RoutedExperts(FeedForward):
+    """m_t = sum over the chosen experts e of g_{t,e} W_down,e (silu(W_gate,e x_t) * (W_up,e x_t)).
+
+    The router: logits z = W_router x in float32, scores s = softmax(z) over all experts; the
+    experts form ``groups`` equal groups of neighbours, a group's score is its largest score and
+    only experts of the ``keep`` best groups can be chosen (``groups`` 1: all can); the ``top``
+    allowed experts with the largest scores are chosen; g = s / (sum of the chosen s + 1e-20) *
+    ``scale``.  Experts have no biases.
+
+    Steps of few rows stream each (row, chosen expert) pair's matrices in one launch; steps of
+    many rows sort the rows by expert and run one matrix product per expert and projection over
+    its rows (``many_rows``: from how many rows on; such steps read the experts' row counts on the
+    host and are never captured).
+    Checkpoint tensors under the prefix: ``router`` [E, hidden]; per expert i ``e<i>.gate``,
+    ``e<i>.up`` [inter, hidden] and ``e<i>.down`` [hidden, inter]."""
+    decode_capturable = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, dtype, device,
+                 groups: int = 1, keep: Optional[int] = None, scale: float = 1.0, many_rows: int = 64,
+                 router_name: str = "router", expert_prefix: str = "e"):
+        keep = groups if keep is None else keep
+        if num_experts % groups or not 1 <= keep <= groups or not 1 <= top <= keep * (num_experts // groups):
+            raise ValueError("experts divide into equal groups, 1 <= keep <= groups, and the kept groups hold "
+                             "at least `top` experts")
+        if num_experts > 512 or top > 32 or groups > 64:
+            raise ValueError("at most 512 experts, 32 chosen per token and 64 groups")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top, self.groups, self.keep = num_experts, top, groups, keep
+        self.scale, self.many_rows = float(scale), int(many_rows)
+        self.router_name, self.expert_prefix = router_name, expert_prefix
+        self.dtype, self.device = dtype, device
+        self.w_router = self.w_gate_up = self.w_down = None
+
+    def kernel_libraries(self, dtype):
+        return [("routed_experts", None), ("elementwise", None)] + ops.gemm_libraries(dtype)
+
+    def param_specs(self, prefix):
+        i, h = self.intermediate_size, self.hidden_size
+        specs = [ParamSpec(prefix + self.router_name, (self.num_experts, h))]
+        for e in range(self.num_experts):
+            p = f"{prefix}{self.expert_prefix}{e}."
+            specs += [ParamSpec(p + "gate", (i, h)), ParamSpec(p + "up", (i, h)), ParamSpec(p + "down", (h, i))]
+        return specs
+
+    def load(self, tensors, prefix):
+        self.w_router = tensors.pop(prefix + self.router_name).contiguous()
+        names = [f"{prefix}{self.expert_prefix}{e}." for e in range(self.num_experts)]
+        # an expert's gate rows followed by its up rows: one product gives both
+        self.w_gate_up = torch.stack([torch.cat([tensors.pop(p + "gate"), tensors.pop(p + "up")], dim=0)
+                                      for p in names]).contiguous()
+        self.w_down = torch.stack([tensors.pop(p + "down") for p in names]).contiguous()
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        logits = ops.linear(x, self.w_router, None, out_dtype=torch.float32)
+        chosen, weights = ops.route(logits, self.top, self.groups, self.keep, self.scale)
+        if T < self.many_rows or getattr(ctx, "captured", False):
+            return ops.expert_rows(x, self.w_gate_up, self.w_down, chosen, weights)
+        return self._sorted(x, chosen, weights)
+
+    def _sorted(self, x, chosen, weights):
+        """Rows sorted by expert, one product per expert and projection over its run of rows."""
+        T = x.shape[0]
+        counts, place = ops.expert_places(chosen, self.num_experts)
+        ends = torch.cumsum(counts, 0, dtype=torch.int32)
+        start = (ends - counts).contiguous()
+        rows = ops.expert_gather(x, chosen, place, start)
+        bounds = ends.tolist()                       # the experts' runs, known on the host
+        hidden = torch.empty((rows.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
+        out = torch.empty_like(rows)
+        lo = 0
+        for e, hi in enumerate(bounds):
+            if hi > lo:
+                gu = ops.linear(rows[lo:hi], self.w_gate_up[e], None, out_dtype=self.dtype)
+                ops.silu_mul(gu, hidden[lo:hi])
+                out[lo:hi] = ops.linear(hidden[lo:hi], self.w_down[e], None, out_dtype=self.dtype)
+            lo = hi
+        return ops.expert_scatter(out, chosen, place, start, weights, T)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
