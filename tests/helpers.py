@@ -146,3 +146,96 @@ def make_gebadra_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str
         w[k] = t.to(w[k].dtype)
     save_file(w, f)
     return str(path)
+
+
+# ---------------------------------------------------------------- Bavetar: tiny configurations
+def _lat(heads, dim, rot_dim, rot_dims, vdim, kv_rank, q_rank, base, scale):
+    return dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=scale,
+                rot=dict(base=base, dims=rot_dims))
+
+
+def _ssm(heads, vdim, state, groups, conv, norm_groups):
+    return dict(heads=heads, vdim=vdim, state=state, groups=groups, conv=conv, norm_groups=norm_groups)
+
+
+def _moe(ff, experts, top, count, keep, scale):
+    return dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top, scale=scale,
+                                                            groups=dict(count=count, keep=keep)))
+
+
+# three heads (the rows of a tile straddle tokens), all head widths different, only half of the rotated
+# part turns, one group of experts (no restriction), a layer without feed-forward, one state group and
+# as many as heads, two and four convolution taps
+BAV_A = dict(
+    architecture="Bavetar", width=64, vocab=300, norm=dict(eps=1e-5), logit_scale=0.7, logit_softcap=9.0,
+    layers=[
+        dict(type="latent_attention", mixer=_lat(3, 16, 8, 4, 24, 40, 24, 10000.0, 0.25), mlp=dict(kind="dense", ff=96)),
+        dict(type="mamba2", mixer=_ssm(4, 16, 24, 1, 4, 4), mlp=_moe(48, 6, 2, 1, 1, 1.0)),
+        dict(type="latent_attention", mixer=_lat(3, 16, 8, 4, 24, 40, 24, 10000.0, 0.25), mlp=None),
+        dict(type="mamba2", mixer=_ssm(2, 40, 80, 2, 2, 1), mlp=dict(kind="dense", ff=72)),
+    ])
+# twenty heads (more than a block's packed rows), five groups of two experts of which two are kept,
+# a state-space layer without feed-forward, three taps, no cap on the logits
+BAV_B = dict(
+    architecture="Bavetar", width=96, vocab=211, norm=dict(eps=1e-6), logit_scale=2.0,
+    layers=[
+        dict(type="mamba2", mixer=_ssm(6, 8, 16, 3, 3, 2), mlp=None),
+        dict(type="latent_attention", mixer=_lat(20, 8, 4, 4, 8, 20, 16, 500.0, 0.3), mlp=_moe(40, 10, 3, 5, 2, 1.5)),
+        dict(type="latent_attention", mixer=_lat(20, 8, 4, 4, 8, 20, 16, 500.0, 0.3), mlp=dict(kind="dense", ff=64)),
+    ])
+# one expert chosen from the one kept group, a state wider than 128, a single tap (no convolution
+# state), eight norm groups, a value wider than the latent
+BAV_C = dict(
+    architecture="Bavetar", width=128, vocab=257, norm=dict(eps=1e-6), logit_scale=1.0, logit_softcap=30.0,
+    layers=[
+        dict(type="latent_attention", mixer=_lat(8, 32, 16, 16, 56, 48, 40, 100000.0, 0.15), mlp=_moe(24, 8, 1, 4, 1, 2.5)),
+        dict(type="mamba2", mixer=_ssm(8, 8, 130, 4, 1, 8), mlp=dict(kind="dense", ff=72)),
+        dict(type="mamba2", mixer=_ssm(4, 24, 32, 4, 4, 2), mlp=_moe(32, 9, 4, 3, 2, 1.0)),
+    ])
+BAVETAR = {"A": (BAV_A, 21, 8), "B": (BAV_B, 22, 16), "C": (BAV_C, 23, 8)}     # config, seed, page tokens
+
+
+def make_bavetar_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str:
+    """A model folder with seeded random weights through the engine's random-weights mode, then
+    reshaped so that no mechanism is a near-identity: projections large enough for sharp softmaxes,
+    decisive routers and gates away from one half; sinks, decay rates, step-size biases and skip
+    terms spread over a range."""
+    from paged_batch_engine_b200.config import load_config
+    from paged_batch_engine_b200.engine.runner import build_model
+    from paged_batch_engine_b200.weights import write_random_model
+    from safetensors.torch import load_file, save_file
+    _, typed = load_config(cfg)
+    model = build_model(typed, torch.float32, "cpu")
+    write_random_model(str(path), typed, model.param_specs(), seed, dtype)
+    f = os.path.join(str(path), "model.safetensors")
+    w = load_file(f)
+    g = torch.Generator().manual_seed(seed)
+    for k in list(w):
+        t = w[k].float()
+        leaf = k.split("mix.")[-1] if ".mix." in k else k.split(".")[-1]
+        latent = k.split(".")[0] + ".mix.uv" in w
+        if leaf in ("dq", "dkv", "uq", "uk", "in") and t.dim() == 2:
+            t = t * 6.0
+        elif leaf in ("uv", "o", "g") and t.dim() == 2:
+            t = t * (12.0 if latent else 4.0)
+        elif leaf in ("up", "down", "gate") and t.dim() == 2:
+            t = t * 4.5
+        elif leaf == "router":
+            t = t * 40.0
+        elif leaf == "sink":
+            t = torch.randn(t.shape, generator=g) * 2.0
+        elif leaf == "A_log":
+            t = torch.log(0.05 + 2.0 * torch.rand(t.shape, generator=g))
+        elif leaf == "dt_bias":
+            t = torch.randn(t.shape, generator=g) * 1.5 - 1.0
+        elif leaf == "D":
+            t = torch.randn(t.shape, generator=g)
+        elif leaf == "conv":
+            t = torch.randn(t.shape, generator=g) * 0.6
+        elif leaf == "conv.b":
+            t = torch.randn(t.shape, generator=g) * 0.2
+        elif k == "embed":
+            t = t * 30.0
+        w[k] = t.to(w[k].dtype)
+    save_file(w, f)
+    return str(path)
