@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """A design beside the engine's closest existing model at equal layer sizes (random weights).
 
-    python bench.py --design gebadra [--steps K] [--warmup W] [--sizes 2048,4096]
+    python bench.py --design gebadra|bavetar [--steps K] [--warmup W] [--sizes 2048,4096]
 
 For each size: prefill (one 2,048-token prompt in one step) and decode (batch 8 from 2,048-token
 contexts, the captured decode step) throughput of a few layers of the design and of a Qwen2 model
@@ -38,12 +38,31 @@ def gebadra_config(width: int) -> dict:
     return dict(architecture="Gebadra", width=width, vocab=32000, streams=2, norm=dict(eps=1e-6), layers=layers)
 
 
-def qwen_config(width: int) -> dict:
-    g = gebadra_config(width)
-    heads = g["layers"][0]["mixer"]["heads"]
+def bavetar_config(width: int) -> dict:
+    """Four layers at the sizes of a real model of this kind: heads of 128 + 64 rotated, a latent of
+    512, state-space heads of 64 with a state of 128, 32 experts of a quarter of the dense width."""
+    heads, ff = width // 128, {2048: 5632, 4096: 11008}.get(width, width * 11 // 4)
+    lat = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=width * 3 // 4, scale=192 ** -0.5,
+               rot=dict(base=1000000.0, dims=64))
+    ssm = dict(heads=width // 32, vdim=64, state=128, groups=8, conv=4, norm_groups=8)
+    dense = dict(kind="dense", ff=ff)
+    moe = dict(kind="moe", expert=dict(ff=ff // 4), router=dict(experts=32, top=4, scale=2.5, groups=dict(count=4, keep=2)))
+    layers = [dict(type="latent_attention", mixer=lat, mlp=dense), dict(type="latent_attention", mixer=lat, mlp=moe),
+              dict(type="mamba2", mixer=ssm, mlp=dense), dict(type="latent_attention", mixer=lat, mlp=moe)][:LAYERS]
+    return dict(architecture="Bavetar", width=width, vocab=32000, norm=dict(eps=1e-6), logit_scale=1.0,
+                logit_softcap=30.0, layers=layers)
+
+
+def qwen_config(width: int, design: str = "gebadra") -> dict:
+    if design == "bavetar":       # as many query heads; the usual eight times fewer key/value heads
+        heads, kv, ff = width // 128, max(1, width // 1024), bavetar_config(width)["layers"][0]["mlp"]["ff"]
+    else:
+        g = gebadra_config(width)
+        heads, kv, ff = g["layers"][0]["mixer"]["heads"], g["layers"][1]["mixer"]["left"]["kv_heads"], \
+            g["layers"][0]["mlp"]["ff"]
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_size=width, num_hidden_layers=LAYERS,
-                num_attention_heads=heads, num_key_value_heads=g["layers"][1]["mixer"]["left"]["kv_heads"], head_dim=128,
-                intermediate_size=g["layers"][0]["mlp"]["ff"], vocab_size=32000, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                num_attention_heads=heads, num_key_value_heads=kv, head_dim=128,
+                intermediate_size=ff, vocab_size=32000, rope_theta=1000000.0, rms_norm_eps=1e-6,
                 tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False, hidden_act="silu",
                 eos_token_id=31999)
 
@@ -160,6 +179,49 @@ def _decode(runner, batch, context, steps, warmup, want_ops=None):
     return ms, per_op, captured
 
 
+def rooflines_bavetar(width: int, pk: dict):
+    """Algorithmic bytes and FLOPs of the compared kernels for the two workloads, per launch."""
+    b = bavetar_config(width)
+    lat, ssm = b["layers"][0]["mixer"], b["layers"][2]["mixer"]
+    H, D, Rr, V, rank, qr = lat["heads"], lat["dim"], lat["rot_dim"], lat["vdim"], lat["kv_rank"], lat["q_rank"]
+    dk = rank + Rr
+    SH, P, N, G = ssm["heads"], ssm["vdim"], ssm["state"], ssm["groups"]
+    chan = SH * P + 2 * G * N
+    ff = b["layers"][0]["mlp"]["ff"]
+    r = b["layers"][1]["mlp"]
+    E, top, eff = r["router"]["experts"], r["router"]["top"], r["expert"]["ff"]
+    q = qwen_config(width, "bavetar")
+    QH, QG = q["num_attention_heads"], q["num_key_value_heads"]
+    T, R, C = PROMPT, BATCH, PROMPT
+
+    def t_us(by, fl):
+        return max(by / (pk["hbm_gbs"] * 1e9), fl / (pk["bf16_tflops"] * 1e12)) * 1e6
+
+    def both(rows, keys_total, keys_read):
+        return {
+            # queries (float32) in, cached rows read once, float32 latent-space outputs; scores over dk and
+            # weighted sums over rank for every (row, head, visible key)
+            "latent_attention": t_us(4 * rows * H * dk + 2 * keys_read * dk + 4 * rows * H * rank,
+                                     2 * H * (dk + rank) * keys_total),
+            "head_product": t_us(2 * rows * H * (D + Rr) + 2 * H * D * rank + 4 * rows * H * dk, 2 * rows * H * D * rank),
+            "latent_prepare": t_us(2 * rows * (qr + dk) * 2, 0),
+            "add2_rmsnorm2": t_us(rows * width * (2 * 4 + 2 * 2 + 2 * 2), 0),
+            "linear_attention": t_us(2 * rows * chan + 4 * rows * SH * (P + 2) + 8 * (R if rows == R else 1) * SH * N * P,
+                                     4 * rows * SH * N * P),
+            "short_conv": t_us(2 * rows * chan * 2, 0),
+            "gated_rms": t_us(rows * SH * P * (4 + 2 + 2), 0),
+            "relu_squared": t_us(rows * ff * 4, 0),
+            "expert_rows": t_us(2 * min(E, rows * top) * 3 * eff * width, 6 * rows * top * eff * width),
+            "route": t_us(rows * E * 4, 0),
+            "paged_attention": t_us(2 * (2 * rows * QH * 128) + 2 * keys_read * QG * 2 * 128, 4 * QH * 128 * keys_total),
+            "attention_decode_fused": t_us(2 * keys_read * QG * 2 * 128, 4 * QH * 128 * keys_total),
+            "add_rmsnorm": t_us(rows * width * (2 * 4 + 2 + 2), 0),
+            "rope_kv_write": t_us(2 * rows * (QH + 2 * QG) * 128 * 2, 0),
+            "silu_mul": t_us(rows * ff * 6, 0),
+        }
+    return {"prefill": both(T, T * (T + 1) // 2, T), "decode": both(R, R * (C + 1), R * (C + 1))}
+
+
 def rooflines(width: int, pk: dict):
     """Algorithmic bytes and FLOPs of the compared kernels for the two workloads, per launch."""
     g = gebadra_config(width)
@@ -197,8 +259,8 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
     from bench import ClockSampler, peaks
     from paged_batch_engine_b200.config import load_config
     from paged_batch_engine_b200.engine.runner import ModelRunner
-    if design != "gebadra":
-        raise SystemExit(f"unknown design {design!r}; known: gebadra")
+    if design not in ("gebadra", "bavetar"):
+        raise SystemExit(f"unknown design {design!r}; known: gebadra, bavetar")
     os.environ["PBE_EXEC"] = "python"        # per-kernel times need every launch to come through ops
     pk = peaks()
     page = 16
@@ -206,13 +268,19 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
     own = ["linear_attention", "pooled_attention", "stream_norm", "gated_rms", "qk_prepare", "pool_blocks",
            "branch_rms_mean"]
     theirs = ["paged_attention", "attention_decode_fused", "add_rmsnorm", "rope_kv_write"]
+    if design == "bavetar":
+        own = ["latent_attention", "head_product", "latent_prepare", "add2_rmsnorm2", "linear_attention", "short_conv",
+               "step_sizes", "gated_rms", "relu_squared", "route", "expert_rows", "expert_places", "expert_gather",
+               "expert_scatter"]
+        theirs = theirs + ["silu_mul"]
+    design_config = bavetar_config if design == "bavetar" else gebadra_config
     sampler = ClockSampler(0)
     sampler.active = True
     out = {}
     for width in sizes:
-        roof = rooflines(width, pk)
+        roof = rooflines_bavetar(width, pk) if design == "bavetar" else rooflines(width, pk)
         row = {}
-        for name, cfg, names in (("gebadra", gebadra_config(width), own), ("qwen2", qwen_config(width), theirs)):
+        for name, cfg, names in ((design, design_config(width), own), ("qwen2", qwen_config(width, design), theirs)):
             _, typed = load_config(cfg)
             runner = ModelRunner.from_random(typed, seed=0, dtype="bfloat16", page_tokens=page, max_cache_tokens=pool,
                                              max_requests=BATCH + 1)
