@@ -351,6 +351,258 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(LatentA
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 sums) for
+// bfloat16 caches whose rows are a multiple of 16 values wide.  A block of four warps takes 16 packed
+// rows and tiles of 32 keys.  The queries are rounded to bfloat16 once (operands of a product, as the
+// cached rows are); scores, maxima, sums and weights are float32.  Per tile: warp w multiplies the
+// queries with keys 8w .. 8w+7, the score blocks meet in shared memory, every warp takes the softmax
+// step of the whole tile for its rows, and multiplies the weights with its own quarter of the value
+// columns.  A weight enters that product as the sum of two bfloat16 numbers (its rounding and the
+// rounding of what is left), so it keeps 16 bits of mantissa, not 8.
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+constexpr int LM_BN = 32;      // keys a tile
+constexpr int LM_WARPS = 4;
+
+// NT: tiles of 8 value columns a warp owns (the four warps cover 32 * NT >= dv columns)
+template <int NT>
+__global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(LatentAttnParams lp) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const AttnParams& p = lp.a;
+  const int DK = lp.dk, DV = lp.dv;
+  const int QSTR = DK + 8;                                   // bfloat16 elements a row of Qs
+  const int wide = max(DK, 32 * NT);
+  const int KSTR = wide + 8;                                 // and of Ks: rows stay 16-byte aligned, banks shift
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][QSTR]
+  __nv_bfloat16* Ks = Qs + LA_BM * QSTR;                                           // [LM_BN][KSTR]
+  float* Ss = reinterpret_cast<float*>(Ks + LM_BN * KSTR);                         // [16][LM_BN + 1]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int32_t* work = p.work + (size_t)blockIdx.x * 4;
+  const int r = work[0];
+  if (r < 0) return;
+  const int split = work[2], nsplit = work[3];
+  const int H = p.num_heads, G = H, P = p.page_tokens;
+  const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
+  const int n_packed = nq * G;
+  const int pr0 = work[1] * p.tile_rows + blockIdx.y * LA_BM;
+  if (pr0 >= n_packed || blockIdx.y * LA_BM >= p.tile_rows) return;
+  const int row_lo = pr0 / G;
+  const int row_hi = (min(n_packed, pr0 + LA_BM) - 1) / G;
+  const int pos0 = sl - nq;
+  const int hi_key = pos0 + row_hi + 1;
+  const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
+  int k_begin = lo_key, k_end = hi_key;
+  if (nsplit > 1) {
+    const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int s0 = lo_req / p.split_keys;
+    k_begin = max(lo_key, (s0 + split) * p.split_keys);
+    k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
+  }
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g8 = lane >> 2, q2 = (lane & 3) * 2;             // the thread's rows g8 and g8 + 8, its column pair
+  const float* q = (const float*)p.q;
+  const __nv_bfloat16* kc = (const __nv_bfloat16*)p.k_cache;
+  const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
+
+  for (int idx = tid; idx < LA_BM * DK; idx += blockDim.x) {
+    const int i = idx / DK, d = idx - i * DK;
+    const int pr = pr0 + i;
+    float v = 0.f;
+    if (pr < n_packed) {
+      const int row = pr / G, hg = pr - row * G;
+      v = q[((size_t)(qs + row) * H + hg) * DK + d];
+    }
+    Qs[i * QSTR + d] = __float2bfloat16_rn(v);
+  }
+  // columns of Ks beyond the cached row (read as value columns that are never stored) stay zero
+  for (int idx = tid; idx < LM_BN * (KSTR - DK); idx += blockDim.x) {
+    const int j = idx / (KSTR - DK), d = DK + idx - j * (KSTR - DK);
+    Ks[j * KSTR + d] = __float2bfloat16_rn(0.f);
+  }
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  int pos_row[2];                                              // the rows' positions, -1: no such row
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int pr = pr0 + g8 + 8 * h;
+    pos_row[h] = pr < n_packed ? pos0 + pr / G : -1;
+  }
+  const int chunks = DK / 8;                                  // 16-byte pieces of a cached row
+  const int col0 = warp * NT * 8;                             // this warp's first value column
+  const int tile0 = (k_begin / LM_BN) * LM_BN;
+  for (int ts = tile0; ts < k_end; ts += LM_BN) {
+    __syncthreads();       // the tile before is consumed (and Qs is written, the first time)
+    for (int idx = tid; idx < LM_BN * chunks; idx += blockDim.x) {
+      const int j = idx / chunks, c = idx - j * chunks;
+      const int key = ts + j;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (key >= k_begin && key < k_end) {
+        const int page = bt[key / P];
+        if (page >= 0) v = *reinterpret_cast<const uint4*>(kc + ((size_t)page * P + (key % P)) * DK + c * 8);
+      }
+      *reinterpret_cast<uint4*>(Ks + j * KSTR + c * 8) = v;
+    }
+    __syncthreads();
+    {
+      // scores of the 16 rows against this warp's eight keys
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* qa = Qs + g8 * QSTR + q2;
+      const __nv_bfloat16* kb = Ks + (warp * 8 + g8) * KSTR + q2;
+      for (int kk = 0; kk < DK; kk += 16) {
+        unsigned a[4];
+        a[0] = *reinterpret_cast<const unsigned*>(qa + kk);
+        a[1] = *reinterpret_cast<const unsigned*>(qa + 8 * QSTR + kk);
+        a[2] = *reinterpret_cast<const unsigned*>(qa + kk + 8);
+        a[3] = *reinterpret_cast<const unsigned*>(qa + 8 * QSTR + kk + 8);
+        const unsigned b0 = *reinterpret_cast<const unsigned*>(kb + kk);
+        const unsigned b1 = *reinterpret_cast<const unsigned*>(kb + kk + 8);
+        mma_bf16(c, a, b0, b1);
+      }
+      float* s0 = Ss + g8 * (LM_BN + 1) + warp * 8 + q2;
+      s0[0] = c[0]; s0[1] = c[1];
+      s0[8 * (LM_BN + 1)] = c[2]; s0[8 * (LM_BN + 1) + 1] = c[3];
+    }
+    __syncthreads();
+    // the softmax step of the whole tile for rows g8 and g8 + 8; this thread holds the weights of
+    // keys q2, q2+1, q2+8, q2+9 (+16 for the tile's second half), as the products' A operand wants
+    unsigned a_hi[2][4], a_lo[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float* srow = Ss + (g8 + 8 * h) * (LM_BN + 1);
+      const int pos = pos_row[h];
+      const int row_lo_key = p.window > 0 ? pos - p.window + 1 : 0;
+      float sc[8];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int col = (i >> 2) * 16 + ((i >> 1) & 1) * 8 + q2 + (i & 1);
+        const int key = ts + col;
+        const bool visible = pos >= 0 && key >= k_begin && key < k_end && key <= pos && key >= row_lo_key;
+        sc[i] = visible ? srow[col] * p.scale : -INFINITY;
+        mx = fmaxf(mx, sc[i]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[h], mx);
+      float alpha = 1.f, sum = 0.f;
+      float pw[8];
+      if (m_new == -INFINITY) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pw[i] = 0.f;
+      } else {
+        alpha = expf(m_run[h] - m_new);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          pw[i] = sc[i] == -INFINITY ? 0.f : expf(sc[i] - m_new);
+          sum += pw[i];
+        }
+        m_run[h] = m_new;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_run[h] = l_run[h] * alpha + sum;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) { acc[i][2 * h] *= alpha; acc[i][2 * h + 1] *= alpha; }
+      // pairs (i, i + 1): half j = i / 4 of the tile, register h (cols q2..) or h + 2 (cols q2 + 8..)
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        const float h0 = __bfloat162float(__float2bfloat16_rn(pw[i])), h1 = __bfloat162float(__float2bfloat16_rn(pw[i + 1]));
+        const int j = i >> 2, reg = h + ((i >> 1) & 1) * 2;
+        a_hi[j][reg] = pack_bf16(h0, h1);
+        a_lo[j][reg] = pack_bf16(pw[i] - h0, pw[i + 1] - h1);
+      }
+    }
+    // weighted values: this warp's columns, the value rows transposed as they are loaded
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const __nv_bfloat16* vrow = Ks + (16 * j + (lane & 15)) * KSTR + col0;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        unsigned b0, b1;
+        const unsigned addr = (unsigned)__cvta_generic_to_shared(vrow + nt * 8);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+        mma_bf16(acc[nt], a_hi[j], b0, b1);
+        mma_bf16(acc[nt], a_lo[j], b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int pr = pr0 + g8 + 8 * h;
+    if (pr >= n_packed) continue;
+    const int row = pr / G, head = pr - row * G;
+    const int t = qs + row;
+    if (nsplit <= 1) {
+      float m_fin = m_run[h], l = l_run[h], factor = 1.f;
+      if (lp.sink) {
+        const float sk = lp.sink[head];
+        m_fin = fmaxf(m_run[h], sk);
+        factor = expf(m_run[h] - m_fin);
+        l = l * factor + expf(sk - m_fin);
+      }
+      const float inv = l > 0.f ? factor / l : 0.f;
+      float* o = (float*)p.out + ((size_t)t * H + head) * DV;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int d = col0 + nt * 8 + q2;
+        if (d < DV) o[d] = acc[nt][2 * h] * inv;
+        if (d + 1 < DV) o[d + 1] = acc[nt][2 * h + 1] * inv;
+      }
+    } else {
+      const int srow = p.tok_split_row[t];
+      const size_t base = ((size_t)srow * H + head) * p.max_splits + split;
+      float* po = p.part_o + base * DV;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int d = col0 + nt * 8 + q2;
+        if (d < DV) po[d] = acc[nt][2 * h];
+        if (d + 1 < DV) po[d + 1] = acc[nt][2 * h + 1];
+      }
+      if (warp == 0 && (lane & 3) == 0) {
+        p.part_ml[base * 2] = m_run[h];
+        p.part_ml[base * 2 + 1] = l_run[h];
+      }
+    }
+  }
+}
+
+template <int NT>
+int launch_latent_mma(const LatentAttnParams& lp, int num_work, cudaStream_t stream) {
+  const int wide = lp.dk > 32 * NT ? lp.dk : 32 * NT;
+  const size_t smem = 2 * ((size_t)LA_BM * (lp.dk + 8) + (size_t)LM_BN * (wide + 8)) + sizeof(float) * LA_BM * (LM_BN + 1);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  static size_t opted = 48 * 1024;
+  if (smem > opted) {
+    cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    opted = 200 * 1024;
+  }
+  dim3 grid(num_work, lp.a.tile_rows / LA_BM);
+  launch_k(latent_attention_mma_kernel<NT>, grid, LM_WARPS * 32, smem, stream, lp);
+  return launch_status();
+}
+
+int dispatch_latent_mma(const LatentAttnParams& lp, int num_work, cudaStream_t stream) {
+  const int nt = (lp.dv + 31) / 32;
+  if (nt <= 1) return launch_latent_mma<1>(lp, num_work, stream);
+  if (nt <= 2) return launch_latent_mma<2>(lp, num_work, stream);
+  if (nt <= 4) return launch_latent_mma<4>(lp, num_work, stream);
+  if (nt <= 8) return launch_latent_mma<8>(lp, num_work, stream);
+  if (nt <= 16) return launch_latent_mma<16>(lp, num_work, stream);
+  return (int)cudaErrorInvalidValue;
+}
+
 struct LatentMergeParams {
   AttnMergeParams m;         // out: float32 [T, H, head_dim]
   const float* sink;
@@ -445,11 +697,13 @@ PBE_EXPORT int pbe_head_product(const void* a, int lda, int ha, int a_dtype, con
   return launch_status();
 }
 
+// tensor_cores: bfloat16 caches with rows a multiple of 16 values wide take the mma.sync kernel
 PBE_EXPORT int pbe_latent_attention(const AttnParams* params, const float* sink, int dk, int dv, int num_work,
-                                    int cache_dtype, cudaStream_t stream) {
+                                    int cache_dtype, int tensor_cores, cudaStream_t stream) {
   if (num_work <= 0) return 0;
   LatentAttnParams lp{*params, sink, dk, dv};
   if (lp.a.tile_rows % LA_BM != 0 || lp.a.split_keys % LA_BN != 0 || dv > dk) return (int)cudaErrorInvalidValue;
+  if (tensor_cores && cache_dtype == PBE_BF16 && dk % 16 == 0) return dispatch_latent_mma(lp, num_work, stream);
   return cache_dtype == PBE_F32 ? dispatch_latent<float>(lp, num_work, stream)
                                 : dispatch_latent<__nv_bfloat16>(lp, num_work, stream);
 }

@@ -6,11 +6,12 @@
 // with the largest scores are chosen (ties: the lower index); their weights are their scores over
 // the sum of the chosen scores (+ 1e-20), times `scale`.  One warp per token.
 //
-// expert_rows: for few rows (decoded tokens).  One block per (token, chosen expert): the
-// expert's gate and up rows are streamed against the token's input (a warp per hidden unit, the
-// lanes along the input), h = silu(g) * u stays in shared memory in float32, the down rows are
-// streamed against it, and the weighted result goes to a slot of its own, [T, top, W]; combine
-// adds a token's slots in order, so a token's result never depends on what else is in the step.
+// expert_rows: for few rows (decoded tokens).  Per (token, chosen expert) pair the expert's gate
+// and up rows are streamed against the token's input (blocks of 32 hidden units, a warp per unit,
+// the lanes along the input in 16-byte loads), h = silu(g) * u goes to scratch memory in float32;
+// a second launch streams the down rows against it (blocks of 32 output columns) and writes the
+// weighted result to the pair's own slot, [T, top, W]; combine adds a token's slots in order, so
+// a token's result never depends on what else is in the step.
 //
 // For many rows the host side sorts the rows by expert (pair_rows / scatter below) and runs one
 // matrix product per expert over its rows.
@@ -132,42 +133,87 @@ struct ExpertRowsParams {
   const void* w_down;        // [E, W, F]
   const int32_t* chosen;     // [T, top]
   const float* weights;      // [T, top]
+  float* hidden;             // [T * top, F] scratch: silu(gate) * up of every pair
   float* part;               // [T, top, W]
   int T, W, F, top;
 };
 
-template <typename T>
-__device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+// dot product of a weight row with a float32 vector in shared memory, the lanes along the row;
+// 16-byte loads of the weights where the row allows them (n a multiple of 8 bfloat16 / 4 float)
+__device__ __forceinline__ float dot_row(const float* __restrict__ w, const float* __restrict__ x, int n, int lane) {
   float a = 0.f;
-  for (int i = lane; i < n; i += 32) a = fmaf(to_float(w[i]), x[i], a);
+  if ((n & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int i = lane * 4; i < n; i += 128) {
+      const float4 v = *reinterpret_cast<const float4*>(w + i);
+      a = fmaf(v.x, x[i], a); a = fmaf(v.y, x[i + 1], a); a = fmaf(v.z, x[i + 2], a); a = fmaf(v.w, x[i + 3], a);
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) a = fmaf(w[i], x[i], a);
+  }
+  return warp_sum(a);
+}
+__device__ __forceinline__ float dot_row(const __nv_bfloat16* __restrict__ w, const float* __restrict__ x, int n,
+                                         int lane) {
+  float a = 0.f;
+  if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int i = lane * 8; i < n; i += 256) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
+      const unsigned u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[j]));
+        a = fmaf(f.x, x[i + 2 * j], a);
+        a = fmaf(f.y, x[i + 2 * j + 1], a);
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) a = fmaf(to_float(w[i]), x[i], a);
+  }
   return warp_sum(a);
 }
 
+constexpr int ER_WARPS = 8;
+constexpr int ER_UNITS = 32;      // hidden units (first kernel) or output columns (second) a block takes
+
+// block (pair, slice of the hidden units): h = silu(W_gate x) * (W_up x) for its units
 template <typename T>
-__global__ void __launch_bounds__(256) expert_rows_kernel(ExpertRowsParams p) {
-  extern __shared__ __align__(16) float sm[];
-  float* xs = sm;            // [W]
-  float* hs = sm + p.W;      // [F]
+__global__ void __launch_bounds__(ER_WARPS * 32) expert_hidden_kernel(ExpertRowsParams p) {
+  extern __shared__ __align__(16) float xs[];        // [W]
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x / p.top, k = blockIdx.x - t * p.top;
-  const int e = p.chosen[(size_t)t * p.top + k];
-  const float weight = p.weights[(size_t)t * p.top + k];
+  const int pair = blockIdx.x;
+  const int t = pair / p.top;
+  const int e = p.chosen[pair];
   const T* x = (const T*)p.x + (size_t)t * p.W;
   for (int i = threadIdx.x; i < p.W; i += blockDim.x) xs[i] = to_float(x[i]);
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* wg = (const T*)p.w_gate + (size_t)e * p.gu_stride;
   const T* wu = (const T*)p.w_up + (size_t)e * p.gu_stride;
-  for (int f = warp; f < p.F; f += warps) {
+  const int f_end = min(p.F, (blockIdx.y + 1) * ER_UNITS);
+  for (int f = blockIdx.y * ER_UNITS + warp; f < f_end; f += ER_WARPS) {
     const float g = dot_row(wg + (size_t)f * p.W, xs, p.W, lane);
     const float u = dot_row(wu + (size_t)f * p.W, xs, p.W, lane);
-    if (lane == 0) hs[f] = (g / (1.0f + expf(-g))) * u;
+    if (lane == 0) p.hidden[(size_t)pair * p.F + f] = (g / (1.0f + expf(-g))) * u;
   }
+}
+
+// block (pair, slice of the output columns): weight * W_down h for its columns
+template <typename T>
+__global__ void __launch_bounds__(ER_WARPS * 32) expert_down_kernel(ExpertRowsParams p) {
+  extern __shared__ __align__(16) float hs[];        // [F]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  const int e = p.chosen[pair];
+  const float weight = p.weights[pair];
+  for (int i = threadIdx.x; i < p.F; i += blockDim.x) hs[i] = p.hidden[(size_t)pair * p.F + i];
   __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* wd = (const T*)p.w_down + (size_t)e * p.W * p.F;
-  float* out = p.part + ((size_t)t * p.top + k) * p.W;
-  for (int c = warp; c < p.W; c += warps) {
+  float* out = p.part + (size_t)pair * p.W;
+  const int c_end = min(p.W, (blockIdx.y + 1) * ER_UNITS);
+  for (int c = blockIdx.y * ER_UNITS + warp; c < c_end; c += ER_WARPS) {
     const float y = dot_row(wd + (size_t)c * p.F, hs, p.F, lane);
     if (lane == 0) out[c] = weight * y;
   }
@@ -259,21 +305,23 @@ PBE_EXPORT int pbe_route(const float* logits, int32_t* chosen, float* weights, i
 }
 
 PBE_EXPORT int pbe_expert_rows(const void* x, const void* w_gate, const void* w_up, long long gu_stride,
-                               const void* w_down,
-                               const int32_t* chosen, const float* weights, float* part, void* out, int dtype, int T,
-                               int W, int F, int top, cudaStream_t stream) {
+                               const void* w_down, const int32_t* chosen, const float* weights, float* hidden,
+                               float* part, void* out, int dtype, int T, int W, int F, int top, cudaStream_t stream) {
   if (T <= 0) return 0;
-  ExpertRowsParams p{x, w_gate, w_up, gu_stride, w_down, chosen, weights, part, T, W, F, top};
-  const size_t smem = sizeof(float) * ((size_t)W + F);
-  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  ExpertRowsParams p{x, w_gate, w_up, gu_stride, w_down, chosen, weights, hidden, part, T, W, F, top};
+  const size_t smem1 = sizeof(float) * (size_t)W, smem2 = sizeof(float) * (size_t)F;
+  if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return (int)cudaErrorInvalidValue;
+  dim3 grid1(T * top, (F + ER_UNITS - 1) / ER_UNITS), grid2(T * top, (W + ER_UNITS - 1) / ER_UNITS);
 #define PBE_ER(TT)                                                                                             \
   do {                                                                                                         \
     static size_t opted = 48 * 1024;                                                                           \
-    if (smem > opted) {                                                                                        \
-      cudaFuncSetAttribute(expert_rows_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);   \
+    if (smem1 > opted || smem2 > opted) {                                                                      \
+      cudaFuncSetAttribute(expert_hidden_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+      cudaFuncSetAttribute(expert_down_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);   \
       opted = 200 * 1024;                                                                                      \
     }                                                                                                          \
-    launch_k(expert_rows_kernel<TT>, T * top, 256, smem, stream, p);                                           \
+    launch_k(expert_hidden_kernel<TT>, grid1, ER_WARPS * 32, smem1, stream, p);                                \
+    launch_k(expert_down_kernel<TT>, grid2, ER_WARPS * 32, smem2, stream, p);                                  \
   } while (0)
   if (dtype == PBE_F32) PBE_ER(float); else PBE_ER(__nv_bfloat16);
 #undef PBE_ER

@@ -1236,6 +1236,9 @@ def step_sizes(u: torch.Tensor, bias: torch.Tensor, rate_log: torch.Tensor):
 
 # ------------------------------------------------------------------ attention over a compressed latent
 LATENT_TILE = 16     # packed rows (row x head) a block of the latent attention kernel takes
+# bfloat16 caches whose rows are a multiple of 16 values wide run on the tensor-core kernel;
+# PBE_LATENT=fma keeps them on the float32-arithmetic kernel (which every other case takes)
+LATENT_FMA = os.environ.get("PBE_LATENT", "").strip().lower() == "fma"
 
 
 def latent_tile_rows(num_heads: int) -> int:
@@ -1333,9 +1336,9 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, sink: Optional[torch.
         window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=0, num_pages=int(cache.shape[0]))
     fn = _fn("latent_attention", "pbe_latent_attention",
-             [ctypes.POINTER(AttnParams), c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(ctypes.byref(p), _ptr(sink), dk, int(value_width), int(meta.num_work), _dtype_code(cache), _stream()),
-           "latent_attention")
+             [ctypes.POINTER(AttnParams), c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(ctypes.byref(p), _ptr(sink), dk, int(value_width), int(meta.num_work), _dtype_code(cache),
+              0 if LATENT_FMA else 1, _stream()), "latent_attention")
     if meta.num_split_rows > 0:
         mp = AttnMergeParams(part_o=part_o.data_ptr(), part_ml=part_ml.data_ptr(), out=out.data_ptr(),
                              split_tokens=meta.split_tokens.data_ptr(), split_counts=meta.split_counts.data_ptr(),
@@ -1383,14 +1386,15 @@ def expert_rows(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
         raise KernelError("expert_rows: rows and expert matrices share a dtype")
     if (W + F) * 4 > 200 * 1024:
         raise KernelError("expert_rows: a row and an expert's hidden units do not fit in shared memory")
+    hidden = torch.empty((T * top, F), dtype=torch.float32, device=x.device)
     part = torch.empty((T, top, W), dtype=torch.float32, device=x.device)
     out = torch.empty((T, W), dtype=x.dtype, device=x.device)
-    fn = _fn("routed_experts", "pbe_expert_rows", [c_void_p] * 3 + [c_ll] + [c_void_p] * 5 + [c_int] * 5 + [c_void_p])
+    fn = _fn("routed_experts", "pbe_expert_rows", [c_void_p] * 3 + [c_ll] + [c_void_p] * 6 + [c_int] * 5 + [c_void_p])
     global _launches
     up = c_void_p(w_gate_up.data_ptr() + F * W * w_gate_up.element_size())
-    _check(fn(_ptr(x), _ptr(w_gate_up), up, 2 * F * W, _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(part),
-              _ptr(out), _dtype_code(x), T, W, F, top, _stream()), "expert_rows")
-    _launches += 1
+    _check(fn(_ptr(x), _ptr(w_gate_up), up, 2 * F * W, _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(hidden),
+              _ptr(part), _ptr(out), _dtype_code(x), T, W, F, top, _stream()), "expert_rows")
+    _launches += 2
     return out
 
 
