@@ -1411,13 +1411,16 @@ def expert_places(chosen: torch.Tensor, num_experts: int):
     return counts, place
 
 
-def expert_gather(x: torch.Tensor, chosen: torch.Tensor, place: torch.Tensor, start: torch.Tensor) -> torch.Tensor:
-    """The rows of x once per chosen expert, sorted by expert: row start[e] + place[pair] = x[t]."""
+def expert_gather(x: torch.Tensor, chosen: torch.Tensor, place: torch.Tensor, start: torch.Tensor,
+                  total_rows: Optional[int] = None) -> torch.Tensor:
+    """The rows of x once per chosen expert, sorted by expert: row start[e] + place[pair] = x[t].
+    ``total_rows``: rows of the result when the experts' runs are padded (rows between the runs are
+    left as they are)."""
     _need_cuda(x, chosen, place, start)
     _need_contiguous(x, chosen, place, start)
     T, W = x.shape
     top = chosen.shape[1]
-    out = torch.empty((T * top, W), dtype=x.dtype, device=x.device)
+    out = torch.empty((total_rows or T * top, W), dtype=x.dtype, device=x.device)
     fn = _fn("routed_experts", "pbe_expert_gather", [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
     _check(fn(_ptr(x), _ptr(chosen), _ptr(place), _ptr(start), _ptr(out), _dtype_code(x), T, top, W, _stream()),
            "expert_gather")
@@ -1436,3 +1439,60 @@ def expert_scatter(y: torch.Tensor, chosen: torch.Tensor, place: torch.Tensor, s
     _check(fn(_ptr(y), _ptr(chosen), _ptr(place), _ptr(start), _ptr(weights), _ptr(out), _dtype_code(y), T, top, W,
               _stream()), "expert_scatter")
     return out
+
+
+# ------------------------------------------------------------------ many small products in one launch
+GROUP_TILE_ROWS = 64     # rows of a tile of the grouped product (runs of rows are padded to it)
+
+
+def _grouped(a, lda, a_group, w, w_group, wk, wn, out, ldo, out_group, T, K, N, groups, tiles, num_tiles,
+             gate=None, rot=0, rot_dims=0, inv_freq=None, positions=None):
+    _need_cuda(a, w, out, tiles, gate, inv_freq, positions)
+    if w.dtype != torch.bfloat16 or (gate is not None and (gate.dtype != torch.bfloat16 or gate.stride(1) != 1)):
+        raise KernelError("grouped product: weights (and the gate) are bfloat16")
+    fn = _fn("grouped_gemm", "pbe_grouped_gemm",
+             [c_void_p, c_int, c_int, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_int, c_int, c_ll, c_int, c_int, c_int,
+              c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    ldg = 0
+    if gate is not None:
+        ldg = gate.stride(0) if T > 1 else max(gate.stride(0), groups)
+    _check(fn(_ptr(a), _dtype_code(a), int(lda), int(a_group), _ptr(w), int(w_group), int(wk), int(wn), _ptr(out),
+              _dtype_code(out), int(ldo), int(out_group), int(T), int(K), int(N), int(groups), _ptr(tiles),
+              int(num_tiles), _ptr(gate), int(ldg), int(rot), int(rot_dims), _ptr(inv_freq), _ptr(positions),
+              _stream()), "grouped_gemm")
+    return out
+
+
+def grouped_heads(a: torch.Tensor, lda: int, head_stride: int, K: int, w: torch.Tensor, w_head_stride: int,
+                  wk: int, wn: int, N: int, out: torch.Tensor, ldo: int, out_head_stride: int, T: int, H: int,
+                  rot: int = 0, rot_dims: int = 0, inv_freq: Optional[torch.Tensor] = None,
+                  positions: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``head_product`` on the tensor cores: the same arguments and result; ``a`` bfloat16 or float32
+    (rounded to bfloat16 as an operand), ``w`` and ``gate`` bfloat16, float32 sums."""
+    return _grouped(a, lda, head_stride, w, w_head_stride, wk, wn, out, ldo, out_head_stride, T, K, N, H, None, 0,
+                    gate, rot, rot_dims, inv_freq, positions)
+
+
+def run_tiles(counts: torch.Tensor, max_tiles: int):
+    """(start int32 [G], tiles int32 [max_tiles, 3]) for rows sorted by group with every group's run
+    padded to whole tiles of ``GROUP_TILE_ROWS``: a group's first row, and per tile (group, first
+    row, rows), idle tiles with group -1."""
+    _need_cuda(counts)
+    G = counts.numel()
+    start = torch.empty(G, dtype=torch.int32, device=counts.device)
+    tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=counts.device)
+    fn = _fn("grouped_gemm", "pbe_run_tiles", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(counts), G, int(max_tiles), _ptr(start), _ptr(tiles), _stream()), "run_tiles")
+    return start, tiles
+
+
+def grouped_runs(a: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """out[row] = W[g] a[row] for the rows of every tile (group g): ``a`` [rows, K] sorted by group,
+    ``w`` bfloat16 [G, N, K], ``tiles`` from ``run_tiles``."""
+    _need_contiguous(a, w, tiles)
+    rows, K = a.shape
+    G, N, _ = w.shape
+    if w.shape[2] != K:
+        raise KernelError("grouped_runs: the weights are [G, N, K]")
+    out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
+    return _grouped(a, K, 0, w, N * K, 1, K, out, N, 0, rows, K, N, G, tiles, tiles.shape[0])

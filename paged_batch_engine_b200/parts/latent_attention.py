@@ -29,6 +29,7 @@ class LatentAttention(Mixer):
     TENSOR_NAMES = dict(dq="dq", dq_norm="dq.norm", uq="uq", dkv="dkv", dkv_norm="dkv.norm", uk="uk", uv="uv",
                         sink="sink", g="g", o="o")
     decode_capturable = True      # stepped from the step's device arrays alone
+    FEW_ROWS = 8                  # steps of at most this many rows keep the per-head products in float32 FMAs
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int, kv_rank: int,
                  q_rank: int, scale: float, eps: float, dtype, device, rotary: Optional[dict] = None,
@@ -68,7 +69,8 @@ class LatentAttention(Mixer):
         return [(self.num_heads, self.tile_rows, self.window)]
 
     def kernel_libraries(self, dtype):
-        return [("latent_attention", None)] + ops.gemm_libraries(dtype)
+        tiled = [("grouped_gemm", None)] if dtype == torch.bfloat16 else []
+        return [("latent_attention", None)] + tiled + ops.gemm_libraries(dtype)
 
     # ---- tensors
     def param_specs(self, prefix):
@@ -118,15 +120,18 @@ class LatentAttention(Mixer):
         q = ops.linear(q_lat, self.w_uq, None, out_dtype=self.dtype, kind=16)           # [T, H * (D + R)]
         # the heads' key maps applied to the queries, the rotated part behind: float32 [T, H, rank + R]
         q_full = torch.empty((T, H, dk), dtype=torch.float32, device=x.device)
-        ops.head_product(q, H * (D + R), D + R, D, self.w_uk, D * rank, rank, 1, rank, q_full, H * dk, dk, T, H,
-                         rot=R, rot_dims=self.rot_dims, inv_freq=self.inv_freq, positions=ctx.positions)
+        # bfloat16 steps of more than a few rows: the per-head products on the tensor cores
+        product = ops.grouped_heads if (T > self.FEW_ROWS and self.w_uk.dtype == torch.bfloat16
+                                        and q.dtype == torch.bfloat16) else ops.head_product
+        product(q, H * (D + R), D + R, D, self.w_uk, D * rank, rank, 1, rank, q_full, H * dk, dk, T, H,
+                rot=R, rot_dims=self.rot_dims, inv_freq=self.inv_freq, positions=ctx.positions)
         meta = ctx.attention_work(cache.group, H, self.tile_rows, self.window, H, rank)
         mixed = ops.latent_attention(q_full, pages, self.sink_logits, meta, H, rank, self.scale, self.window,
                                      ctx.page_tokens)                                   # float32 [T, H, rank]
         # the heads' value maps applied to the attention's output, times the heads' gates
         out = torch.empty((T, H * V), dtype=self.dtype, device=x.device)
         gate = down[:, qr + dk:] if self.out_gate else None
-        ops.head_product(mixed, H * rank, rank, rank, self.w_uv, V * rank, 1, rank, V, out, H * V, V, T, H, gate=gate)
+        product(mixed, H * rank, rank, rank, self.w_uv, V * rank, 1, rank, V, out, H * V, V, T, H, gate=gate)
         return ops.linear(out, self.w_o, None, out_dtype=self.dtype, kind=2)
 
 

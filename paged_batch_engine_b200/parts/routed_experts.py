@@ -19,13 +19,16 @@ class RoutedExperts(FeedForward):
     allowed experts with the largest scores are chosen; g = s / (sum of the chosen s + 1e-20) *
     ``scale``.  Experts have no biases.
 
-    Steps of few rows stream each (row, chosen expert) pair's matrices in one launch; steps of
-    many rows sort the rows by expert and run one matrix product per expert and projection over
-    its rows (``many_rows``: from how many rows on; such steps read the experts' row counts on the
-    host and are never captured).
+    Steps of few rows stream each (row, chosen expert) pair's matrices; steps of many rows sort the
+    rows by expert.  In bfloat16 every expert's run is padded to whole row tiles and one launch per
+    projection multiplies each tile with its expert's matrix on the tensor cores, all on the
+    device.  In float32 one product per expert and projection runs over its rows (``many_rows``:
+    from how many rows on; such steps read the experts' row counts on the host and are never
+    captured).
     Checkpoint tensors under the prefix: ``router`` [E, hidden]; per expert i ``e<i>.gate``,
     ``e<i>.up`` [inter, hidden] and ``e<i>.down`` [hidden, inter]."""
     decode_capturable = True
+    MANY_ROWS_TILED = 16       # bfloat16 steps of at least this many rows take the tiled products
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int, dtype, device,
                  groups: int = 1, keep: Optional[int] = None, scale: float = 1.0, many_rows: int = 64,
@@ -44,7 +47,8 @@ class RoutedExperts(FeedForward):
         self.w_router = self.w_gate_up = self.w_down = None
 
     def kernel_libraries(self, dtype):
-        return [("routed_experts", None), ("elementwise", None)] + ops.gemm_libraries(dtype)
+        tiled = [("grouped_gemm", None)] if dtype == torch.bfloat16 else []
+        return [("routed_experts", None), ("elementwise", None)] + tiled + ops.gemm_libraries(dtype)
 
     def param_specs(self, prefix):
         i, h = self.intermediate_size, self.hidden_size
@@ -66,9 +70,28 @@ class RoutedExperts(FeedForward):
         T = x.shape[0]
         logits = ops.linear(x, self.w_router, None, out_dtype=torch.float32)
         chosen, weights = ops.route(logits, self.top, self.groups, self.keep, self.scale)
+        if x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16:
+            if T < min(self.many_rows, self.MANY_ROWS_TILED):
+                return ops.expert_rows(x, self.w_gate_up, self.w_down, chosen, weights)
+            return self._tiled(x, chosen, weights)
         if T < self.many_rows or getattr(ctx, "captured", False):
             return ops.expert_rows(x, self.w_gate_up, self.w_down, chosen, weights)
         return self._sorted(x, chosen, weights)
+
+    def _tiled(self, x, chosen, weights):
+        """bfloat16: rows sorted by expert, every expert's run padded to whole row tiles, and one
+        launch per projection that multiplies every tile with its expert's matrix on the tensor
+        cores.  Nothing is read on the host."""
+        T = x.shape[0]
+        counts, place = ops.expert_places(chosen, self.num_experts)
+        max_tiles = (T * self.top + ops.GROUP_TILE_ROWS - 1) // ops.GROUP_TILE_ROWS + self.num_experts
+        start, tiles = ops.run_tiles(counts, max_tiles)
+        rows = ops.expert_gather(x, chosen, place, start, total_rows=max_tiles * ops.GROUP_TILE_ROWS)
+        gu = ops.grouped_runs(rows, self.w_gate_up, tiles, self.dtype)
+        hidden = torch.empty((rows.shape[0], self.intermediate_size), dtype=self.dtype, device=x.device)
+        ops.silu_mul(gu, hidden)
+        out = ops.grouped_runs(hidden, self.w_down, tiles, self.dtype)
+        return ops.expert_scatter(out, chosen, place, start, weights, T)
 
     def _sorted(self, x, chosen, weights):
         """Rows sorted by expert, one product per expert and projection over its run of rows."""

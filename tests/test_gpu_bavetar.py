@@ -225,8 +225,9 @@ def test_expert_rows_and_rows_sorted_by_expert(W, F, E, top, dtype):
     x = torch.randn(T, W, generator=g).to(dtype)
     want = pb.routed_ff(x.double(), {k: v.double() for k, v in w.items()}, "p.",
                         dict(router=dict(experts=E, top=top, scale=1.3)))
+    part.MANY_ROWS_TILED = 1 << 30                 # every row streams its experts' matrices
     by_rows = part.forward(x.to(DEV), None).float().cpu().double()
-    part.many_rows = 1
+    part.many_rows = part.MANY_ROWS_TILED = 1      # rows sorted by expert (bfloat16: the tiled products)
     by_expert = part.forward(x.to(DEV), None).float().cpu().double()
     tol = 3e-5 if dtype == torch.float32 else 6e-2
     scale = float(want.abs().max())
