@@ -271,7 +271,7 @@ def run(design: str, steps: int, warmup: int, sizes=(2048, 4096)) -> dict:
     if design == "bavetar":
         own = ["latent_attention", "head_product", "latent_prepare", "add2_rmsnorm2", "linear_attention", "short_conv",
                "step_sizes", "gated_rms", "relu_squared", "route", "expert_rows", "expert_places", "expert_gather",
-               "expert_scatter"]
+               "expert_scatter", "grouped_heads", "grouped_runs", "run_tiles"]
         theirs = theirs + ["silu_mul"]
     design_config = bavetar_config if design == "bavetar" else gebadra_config
     sampler = ClockSampler(0)

@@ -21,7 +21,7 @@
 using namespace pbe;
 
 namespace {
-constexpr int GG_BM = 64, GG_BN = 64, GG_BK = 32, GG_PAD = 8;
+constexpr int GG_BM = 64, GG_BN = 128, GG_BK = 32, GG_PAD = 8;
 
 struct GroupGemmParams {
   const void* a;
@@ -51,10 +51,20 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
 __device__ __forceinline__ __nv_bfloat16 as_bf16(float v) { return __float2bfloat16_rn(v); }
 __device__ __forceinline__ __nv_bfloat16 as_bf16(__nv_bfloat16 v) { return v; }
 
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const __nv_bfloat16* row) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// A block of four warps makes a 64 x 128 tile of the output, every warp a 32 x 64 corner of it; the
+// operands of the next 32 values of K wait in registers while the current ones are multiplied out of
+// shared memory (two buffers, one barrier a step); fragments come by ldmatrix.
 template <typename TA, typename TO>
 __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
-  __shared__ __align__(16) __nv_bfloat16 As[GG_BM][GG_BK + GG_PAD];
-  __shared__ __align__(16) __nv_bfloat16 Ws[GG_BN][GG_BK + GG_PAD];
+  constexpr int STR = GG_BK + GG_PAD;
+  __shared__ __align__(16) __nv_bfloat16 As[2][GG_BM][STR];
+  __shared__ __align__(16) __nv_bfloat16 Ws[2][GG_BN][STR];
   pdl_launch_dependents();
   pdl_wait();
   int g, row0, rows;
@@ -70,21 +80,24 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
   const int n0 = blockIdx.z * GG_BN;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g8 = lane >> 2, q2 = (lane & 3) * 2;
-  const int wm = (warp >> 1) * 32, wn0 = (warp & 1) * 32;      // the warp's 32 x 32 corner of the tile
+  const int wm = (warp >> 1) * 32, wn0 = (warp & 1) * 64;      // the warp's 32 x 64 corner of the tile
   const TA* a = (const TA*)p.a + (size_t)g * p.a_group;
   const __nv_bfloat16* w = p.w + (size_t)g * p.w_group;
-  float acc[2][4][4];
+  float acc[2][8][4];
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
   const bool a_vec = (p.lda % 8 == 0) && (p.a_group % 8 == 0) && ((uintptr_t)p.a % 16 == 0);
   const bool w_vec = ((p.wk == 1 ? p.wn : p.wk) % 8 == 0) && (p.w_group % 8 == 0) && ((uintptr_t)p.w % 16 == 0);
-  for (int k0 = 0; k0 < p.K; k0 += GG_BK) {
-    // A: 64 rows x 4 pieces of 8 values
-    for (int idx = tid; idx < GG_BM * (GG_BK / 8); idx += 128) {
-      const int i = idx >> 2, kc = (idx & 3) * 8;
-      const int k = k0 + kc;
+  constexpr int A_PER = GG_BM * (GG_BK / 8) / 128;             // 16-byte pieces a thread stages: 2 of A
+  constexpr int W_PER = GG_BN * (GG_BK / 8) / 128;             // and 4 of W
+  uint4 ra[A_PER], rw[W_PER];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int x = 0; x < A_PER; ++x) {
+      const int idx = tid + x * 128;
+      const int i = idx >> 2, k = k0 + (idx & 3) * 8;
       __nv_bfloat16 v[8];
       const TA* src = a + (size_t)(row0 + i) * p.lda + k;
       if (i < rows && k + 8 <= p.K && a_vec) {
@@ -99,14 +112,14 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = (i < rows && k + j < p.K) ? as_bf16(src[j]) : as_bf16(0.f);
       }
-      *reinterpret_cast<uint4*>(&As[i][kc]) = *reinterpret_cast<const uint4*>(v);
+      ra[x] = *reinterpret_cast<const uint4*>(v);
     }
-    // W: staged as [n][k] whichever way it lies
-    if (p.wk == 1) {
-      for (int idx = tid; idx < GG_BN * (GG_BK / 8); idx += 128) {
-        const int n = idx >> 2, kc = (idx & 3) * 8;
-        const int k = k0 + kc;
-        __nv_bfloat16 v[8];
+#pragma unroll
+    for (int x = 0; x < W_PER; ++x) {
+      const int idx = tid + x * 128;
+      __nv_bfloat16 v[8];
+      if (p.wk == 1) {                     // [N, K]: eight values of K of one output column
+        const int n = idx >> 2, k = k0 + (idx & 3) * 8;
         const __nv_bfloat16* src = w + (size_t)(n0 + n) * p.wn + k;
         if (n0 + n < p.N && k + 8 <= p.K && w_vec) {
           *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(src);
@@ -114,12 +127,8 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = (n0 + n < p.N && k + j < p.K) ? src[j] : as_bf16(0.f);
         }
-        *reinterpret_cast<uint4*>(&Ws[n][kc]) = *reinterpret_cast<const uint4*>(v);
-      }
-    } else {
-      for (int idx = tid; idx < GG_BK * (GG_BN / 8); idx += 128) {
-        const int k = idx >> 3, nc = (idx & 7) * 8;
-        __nv_bfloat16 v[8];
+      } else {                             // [K, N]: eight output columns of one value of K
+        const int k = idx >> 4, nc = (idx & 15) * 8;
         const __nv_bfloat16* src = w + (size_t)(k0 + k) * p.wk + (size_t)(n0 + nc) * p.wn;
         if (k0 + k < p.K && n0 + nc + 8 <= p.N && w_vec && p.wn == 1) {
           *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(src);
@@ -128,33 +137,54 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
           for (int j = 0; j < 8; ++j)
             v[j] = (k0 + k < p.K && n0 + nc + j < p.N) ? src[(size_t)j * p.wn] : as_bf16(0.f);
         }
+      }
+      rw[x] = *reinterpret_cast<const uint4*>(v);
+    }
+  };
+  auto stash = [&](int buf) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) Ws[nc + j][k] = v[j];
+    for (int x = 0; x < A_PER; ++x) {
+      const int idx = tid + x * 128;
+      *reinterpret_cast<uint4*>(&As[buf][idx >> 2][(idx & 3) * 8]) = ra[x];
+    }
+#pragma unroll
+    for (int x = 0; x < W_PER; ++x) {
+      const int idx = tid + x * 128;
+      if (p.wk == 1) {
+        *reinterpret_cast<uint4*>(&Ws[buf][idx >> 2][(idx & 3) * 8]) = rw[x];
+      } else {
+        const int k = idx >> 4, nc = (idx & 15) * 8;
+        const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&rw[x]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) Ws[buf][nc + j][k] = v[j];
       }
     }
-    __syncthreads();
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < p.K; k0 += GG_BK, buf ^= 1) {
+    const bool more = k0 + GG_BK < p.K;
+    if (more) fetch(k0 + GG_BK);
 #pragma unroll
     for (int kk = 0; kk < GG_BK; kk += 16) {
-      unsigned af[2][4], bf[4][2];
+      unsigned af[2][4], bf[4][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const __nv_bfloat16* r0 = &As[wm + i * 16 + g8][kk + q2];
-        af[i][0] = *reinterpret_cast<const unsigned*>(r0);
-        af[i][1] = *reinterpret_cast<const unsigned*>(r0 + 8 * (GG_BK + GG_PAD));
-        af[i][2] = *reinterpret_cast<const unsigned*>(r0 + 8);
-        af[i][3] = *reinterpret_cast<const unsigned*>(r0 + 8 * (GG_BK + GG_PAD) + 8);
-      }
+      for (int i = 0; i < 2; ++i)
+        ldmatrix_x4(af[i], &As[buf][wm + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __nv_bfloat16* c0 = &Ws[wn0 + j * 8 + g8][kk + q2];
-        bf[j][0] = *reinterpret_cast<const unsigned*>(c0);
-        bf[j][1] = *reinterpret_cast<const unsigned*>(c0 + 8);
-      }
+      for (int j = 0; j < 4; ++j)       // two tiles of eight columns a load: {b0, b1} of the first, then of the second
+        ldmatrix_x4(bf[j], &Ws[buf][wn0 + j * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma16816(acc[i][j], af[i], bf[j][0], bf[j][1]);
+        for (int j = 0; j < 4; ++j) {
+          mma16816(acc[i][2 * j], af[i], bf[j][0], bf[j][1]);
+          mma16816(acc[i][2 * j + 1], af[i], bf[j][2], bf[j][3]);
+        }
     }
+    if (more) stash(buf ^ 1);          // the other buffer: its readers passed the barrier of the step before
     __syncthreads();
   }
   TO* out = (TO*)p.out + (size_t)g * p.out_group;
@@ -168,7 +198,7 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(GroupGemmParams p) {
       float gate = 1.f;
       if (p.gate) gate = 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)t * p.ldg + g])));
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 8; ++j) {
         const int n = n0 + wn0 + j * 8 + q2;
         if (n < p.N) out[(size_t)t * p.ldo + n] = from_float<TO>(acc[i][j][2 * hh] * gate);
         if (n + 1 < p.N) out[(size_t)t * p.ldo + n + 1] = from_float<TO>(acc[i][j][2 * hh + 1] * gate);

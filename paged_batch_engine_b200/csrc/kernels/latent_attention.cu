@@ -353,8 +353,10 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(LatentA
 
 // ------------------------------------------------------------------------------------------------
 // The same attention on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 sums) for
-// bfloat16 caches whose rows are a multiple of 16 values wide.  A block of four warps takes 16 packed
-// rows and tiles of 32 keys.  The queries are rounded to bfloat16 once (operands of a product, as the
+// bfloat16 caches whose rows are a multiple of 16 values wide.  Four warps take 16 packed rows and
+// tiles of 32 keys; a block is RG such groups of four warps (16 RG rows) that share every key tile,
+// so the tile crosses from the L2 cache once for all of them: one group for decoded tokens, four for
+// prompt portions.  The queries are rounded to bfloat16 once (operands of a product, as the
 // cached rows are); scores, maxima, sums and weights are float32.  Per tile: warp w multiplies the
 // queries with keys 8w .. 8w+7, the score blocks meet in shared memory, every warp takes the softmax
 // step of the whole tile for its rows, and multiplies the weights with its own quarter of the value
@@ -373,18 +375,19 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 constexpr int LM_BN = 32;      // keys a tile
 constexpr int LM_WARPS = 4;
 
-// NT: tiles of 8 value columns a warp owns (the four warps cover 32 * NT >= dv columns)
-template <int NT>
-__global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(LatentAttnParams lp) {
+// NT: tiles of 8 value columns a warp owns (four warps cover 32 * NT >= dv columns); RG: row groups
+template <int NT, int RG>
+__global__ void __launch_bounds__(LM_WARPS * 32 * RG) latent_attention_mma_kernel(LatentAttnParams lp) {
+  constexpr int ROWS = LA_BM * RG;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const AttnParams& p = lp.a;
   const int DK = lp.dk, DV = lp.dv;
   const int QSTR = DK + 8;                                   // bfloat16 elements a row of Qs
   const int wide = max(DK, 32 * NT);
   const int KSTR = wide + 8;                                 // and of Ks: rows stay 16-byte aligned, banks shift
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][QSTR]
-  __nv_bfloat16* Ks = Qs + LA_BM * QSTR;                                           // [LM_BN][KSTR]
-  float* Ss = reinterpret_cast<float*>(Ks + LM_BN * KSTR);                         // [16][LM_BN + 1]
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [ROWS][QSTR]
+  __nv_bfloat16* Kbuf = Qs + ROWS * QSTR;                                          // [2][LM_BN][KSTR]
+  float* Ss = reinterpret_cast<float*>(Kbuf + 2 * LM_BN * KSTR);                   // [ROWS][LM_BN + 1]
   pdl_launch_dependents();
   pdl_wait();
   const int32_t* work = p.work + (size_t)blockIdx.x * 4;
@@ -394,10 +397,10 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
   const int H = p.num_heads, G = H, P = p.page_tokens;
   const int qs = p.q_start[r], nq = p.q_len[r], sl = p.seq_len[r];
   const int n_packed = nq * G;
-  const int pr0 = work[1] * p.tile_rows + blockIdx.y * LA_BM;
-  if (pr0 >= n_packed || blockIdx.y * LA_BM >= p.tile_rows) return;
+  const int pr0 = work[1] * p.tile_rows + blockIdx.y * ROWS;
+  if (pr0 >= n_packed || blockIdx.y * ROWS >= p.tile_rows) return;
   const int row_lo = pr0 / G;
-  const int row_hi = (min(n_packed, pr0 + LA_BM) - 1) / G;
+  const int row_hi = (min(n_packed, pr0 + ROWS) - 1) / G;
   const int pos0 = sl - nq;
   const int hi_key = pos0 + row_hi + 1;
   const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
@@ -408,13 +411,14 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
     k_begin = max(lo_key, (s0 + split) * p.split_keys);
     k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
   }
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g8 = lane >> 2, q2 = (lane & 3) * 2;             // the thread's rows g8 and g8 + 8, its column pair
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = (tid >> 5) & 3, rg = tid >> 7;            // the warp's place in its group of four, and the group
+  const int g8 = lane >> 2, q2 = (lane & 3) * 2;             // the thread's rows g8 and g8 + 8 of the group, its column pair
   const float* q = (const float*)p.q;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)p.k_cache;
   const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
 
-  for (int idx = tid; idx < LA_BM * DK; idx += blockDim.x) {
+  for (int idx = tid; idx < ROWS * DK; idx += blockDim.x) {
     const int i = idx / DK, d = idx - i * DK;
     const int pr = pr0 + i;
     float v = 0.f;
@@ -424,10 +428,10 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
     }
     Qs[i * QSTR + d] = __float2bfloat16_rn(v);
   }
-  // columns of Ks beyond the cached row (read as value columns that are never stored) stay zero
-  for (int idx = tid; idx < LM_BN * (KSTR - DK); idx += blockDim.x) {
+  // columns of the key tiles beyond the cached row (read as value columns that are never stored) stay zero
+  for (int idx = tid; idx < 2 * LM_BN * (KSTR - DK); idx += blockDim.x) {
     const int j = idx / (KSTR - DK), d = DK + idx - j * (KSTR - DK);
-    Ks[j * KSTR + d] = __float2bfloat16_rn(0.f);
+    Kbuf[j * KSTR + d] = __float2bfloat16_rn(0.f);
   }
   float acc[NT][4];
 #pragma unroll
@@ -436,29 +440,48 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
   int pos_row[2];                                              // the rows' positions, -1: no such row
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int pr = pr0 + g8 + 8 * h;
+    const int pr = pr0 + rg * LA_BM + g8 + 8 * h;
     pos_row[h] = pr < n_packed ? pos0 + pr / G : -1;
   }
   const int chunks = DK / 8;                                  // 16-byte pieces of a cached row
   const int col0 = warp * NT * 8;                             // this warp's first value column
   const int tile0 = (k_begin / LM_BN) * LM_BN;
-  for (int ts = tile0; ts < k_end; ts += LM_BN) {
-    __syncthreads();       // the tile before is consumed (and Qs is written, the first time)
-    for (int idx = tid; idx < LM_BN * chunks; idx += blockDim.x) {
-      const int j = idx / chunks, c = idx - j * chunks;
-      const int key = ts + j;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (key >= k_begin && key < k_end) {
-        const int page = bt[key / P];
-        if (page >= 0) v = *reinterpret_cast<const uint4*>(kc + ((size_t)page * P + (key % P)) * DK + c * 8);
+  // A tile's rows arrive by asynchronous 16-byte copies, four threads a row (its page is looked up
+  // once), into the buffer that is not being multiplied: the tile after this one is on its way while
+  // this one is worked on.
+  auto fetch = [&](int buf, int ts) {
+    constexpr int PER_ROW = 4 * RG;      // threads that share a row
+    const int j = tid / PER_ROW, key = ts + j;
+    int page = -1;
+    if (key >= k_begin && key < k_end) page = bt[key / P];
+    __nv_bfloat16* dst = Kbuf + ((size_t)buf * LM_BN + j) * KSTR;
+    if (page >= 0) {
+      const __nv_bfloat16* src = kc + ((size_t)page * P + (key % P)) * DK;
+      for (int c = tid % PER_ROW; c < chunks; c += PER_ROW) {
+        const unsigned to = (unsigned)__cvta_generic_to_shared(dst + c * 8);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to), "l"(src + c * 8) : "memory");
       }
-      *reinterpret_cast<uint4*>(Ks + j * KSTR + c * 8) = v;
+    } else {
+      for (int c = tid % PER_ROW; c < chunks; c += PER_ROW) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (tile0 < k_end) fetch(0, tile0);
+  int buf = 0;
+  for (int ts = tile0; ts < k_end; ts += LM_BN, buf ^= 1) {
+    __syncthreads();       // the tile before is consumed (and Qs is written, the first time)
+    const __nv_bfloat16* Ks = Kbuf + (size_t)buf * LM_BN * KSTR;
+    if (ts + LM_BN < k_end) {
+      fetch(buf ^ 1, ts + LM_BN);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     {
       // scores of the 16 rows against this warp's eight keys
       float c[4] = {0.f, 0.f, 0.f, 0.f};
-      const __nv_bfloat16* qa = Qs + g8 * QSTR + q2;
+      const __nv_bfloat16* qa = Qs + (rg * LA_BM + g8) * QSTR + q2;
       const __nv_bfloat16* kb = Ks + (warp * 8 + g8) * KSTR + q2;
       for (int kk = 0; kk < DK; kk += 16) {
         unsigned a[4];
@@ -470,7 +493,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
         const unsigned b1 = *reinterpret_cast<const unsigned*>(kb + kk + 8);
         mma_bf16(c, a, b0, b1);
       }
-      float* s0 = Ss + g8 * (LM_BN + 1) + warp * 8 + q2;
+      float* s0 = Ss + (rg * LA_BM + g8) * (LM_BN + 1) + warp * 8 + q2;
       s0[0] = c[0]; s0[1] = c[1];
       s0[8 * (LM_BN + 1)] = c[2]; s0[8 * (LM_BN + 1) + 1] = c[3];
     }
@@ -480,7 +503,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
     unsigned a_hi[2][4], a_lo[2][4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const float* srow = Ss + (g8 + 8 * h) * (LM_BN + 1);
+      const float* srow = Ss + (rg * LA_BM + g8 + 8 * h) * (LM_BN + 1);
       const int pos = pos_row[h];
       const int row_lo_key = p.window > 0 ? pos - p.window + 1 : 0;
       float sc[8];
@@ -540,7 +563,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
   }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int pr = pr0 + g8 + 8 * h;
+    const int pr = pr0 + rg * LA_BM + g8 + 8 * h;
     if (pr >= n_packed) continue;
     const int row = pr / G, head = pr - row * G;
     const int t = qs + row;
@@ -578,28 +601,36 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_attention_mma_kernel(Lat
   }
 }
 
-template <int NT>
+template <int NT, int RG>
 int launch_latent_mma(const LatentAttnParams& lp, int num_work, cudaStream_t stream) {
+  constexpr int ROWS = LA_BM * RG;
   const int wide = lp.dk > 32 * NT ? lp.dk : 32 * NT;
-  const size_t smem = 2 * ((size_t)LA_BM * (lp.dk + 8) + (size_t)LM_BN * (wide + 8)) + sizeof(float) * LA_BM * (LM_BN + 1);
+  const size_t smem = 2 * ((size_t)ROWS * (lp.dk + 8) + 2 * (size_t)LM_BN * (wide + 8)) + sizeof(float) * ROWS * (LM_BN + 1);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   static size_t opted = 48 * 1024;
   if (smem > opted) {
-    cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_mma_kernel<NT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     opted = 200 * 1024;
   }
-  dim3 grid(num_work, lp.a.tile_rows / LA_BM);
-  launch_k(latent_attention_mma_kernel<NT>, grid, LM_WARPS * 32, smem, stream, lp);
+  dim3 grid(num_work, (lp.a.tile_rows + ROWS - 1) / ROWS);
+  launch_k(latent_attention_mma_kernel<NT, RG>, grid, LM_WARPS * 32 * RG, smem, stream, lp);
   return launch_status();
 }
 
-int dispatch_latent_mma(const LatentAttnParams& lp, int num_work, cudaStream_t stream) {
+// wide_blocks: blocks of four row groups (prompt portions) when the work list's tiles hold 64 rows
+int dispatch_latent_mma(const LatentAttnParams& lp, int num_work, bool wide_blocks, cudaStream_t stream) {
   const int nt = (lp.dv + 31) / 32;
-  if (nt <= 1) return launch_latent_mma<1>(lp, num_work, stream);
-  if (nt <= 2) return launch_latent_mma<2>(lp, num_work, stream);
-  if (nt <= 4) return launch_latent_mma<4>(lp, num_work, stream);
-  if (nt <= 8) return launch_latent_mma<8>(lp, num_work, stream);
-  if (nt <= 16) return launch_latent_mma<16>(lp, num_work, stream);
+  const size_t wide_smem = 2 * ((size_t)64 * (lp.dk + 8) + 2 * (size_t)LM_BN * ((lp.dk > 32 * nt ? lp.dk : 32 * nt) + 8)) +
+                           sizeof(float) * 64 * (LM_BN + 1);
+  const bool four = wide_blocks && lp.a.tile_rows % 64 == 0 && wide_smem <= 200 * 1024;
+#define PBE_LM(N)                                                                                   \
+  return four ? launch_latent_mma<N, 4>(lp, num_work, stream) : launch_latent_mma<N, 1>(lp, num_work, stream)
+  if (nt <= 1) { PBE_LM(1); }
+  if (nt <= 2) { PBE_LM(2); }
+  if (nt <= 4) { PBE_LM(4); }
+  if (nt <= 8) { PBE_LM(8); }
+  if (nt <= 16) { PBE_LM(16); }
+#undef PBE_LM
   return (int)cudaErrorInvalidValue;
 }
 
@@ -698,12 +729,14 @@ PBE_EXPORT int pbe_head_product(const void* a, int lda, int ha, int a_dtype, con
 }
 
 // tensor_cores: bfloat16 caches with rows a multiple of 16 values wide take the mma.sync kernel
+// (1: blocks of 16 rows, for decoded tokens; 2: blocks of 64 rows, for prompt portions)
 PBE_EXPORT int pbe_latent_attention(const AttnParams* params, const float* sink, int dk, int dv, int num_work,
                                     int cache_dtype, int tensor_cores, cudaStream_t stream) {
   if (num_work <= 0) return 0;
   LatentAttnParams lp{*params, sink, dk, dv};
   if (lp.a.tile_rows % LA_BM != 0 || lp.a.split_keys % LA_BN != 0 || dv > dk) return (int)cudaErrorInvalidValue;
-  if (tensor_cores && cache_dtype == PBE_BF16 && dk % 16 == 0) return dispatch_latent_mma(lp, num_work, stream);
+  if (tensor_cores && cache_dtype == PBE_BF16 && dk % 16 == 0)
+    return dispatch_latent_mma(lp, num_work, tensor_cores == 2, stream);
   return cache_dtype == PBE_F32 ? dispatch_latent<float>(lp, num_work, stream)
                                 : dispatch_latent<__nv_bfloat16>(lp, num_work, stream);
 }

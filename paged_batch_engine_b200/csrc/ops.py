@@ -1182,13 +1182,17 @@ def scale_softcap(logits: torch.Tensor, scale: float, cap: Optional[float]) -> t
 # ------------------------------------------------------------------ short convolution, step sizes
 def short_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
                request_of_row: torch.Tensor, q_start: torch.Tensor, q_len: torch.Tensor, slots: torch.Tensor,
-               num_requests: int, silu: bool = True, update_state: bool = True) -> torch.Tensor:
+               num_requests: int, silu: bool = True, update_state: bool = True,
+               weight_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal convolution per channel over each request's rows: ``u`` [T, C] a column slice of a
     projection, ``weight`` float32 [C, taps] (last column: the current token), ``state`` float32
-    [slots, taps - 1, C] holding each request's last inputs (read, then moved on).  Returns
-    [T, C] in u's dtype."""
-    _need_cuda(u, weight, bias, state, request_of_row, q_start, q_len, slots)
-    _need_contiguous(weight, bias, state)
+    [slots, taps - 1, C] holding each request's last inputs (read, then moved on).  ``weight_t``:
+    the same weights as float32 [taps, C], for the kernel that takes eight channels a thread.
+    Returns [T, C] in u's dtype."""
+    _need_cuda(u, weight, bias, state, request_of_row, q_start, q_len, slots, weight_t)
+    _need_contiguous(weight, bias, state, weight_t)
+    if weight_t is not None and (weight_t.dtype != torch.float32 or tuple(weight_t.shape) != (weight.shape[1], u.shape[1])):
+        raise KernelError("short_conv: weight_t is float32 [taps, C]")
     _column_slice(u, "short_conv")
     T, C = u.shape
     taps = weight.shape[1]
@@ -1206,9 +1210,9 @@ def short_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     ld = u.stride(0) if T > 1 else max(u.stride(0), C)
     fn = _fn("short_conv", "pbe_short_conv",
              [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     global _launches
-    _check(fn(_ptr(u), ld, _dtype_code(u), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(request_of_row),
+    _check(fn(_ptr(u), ld, _dtype_code(u), _ptr(weight), _ptr(weight_t), _ptr(bias), _ptr(state), _ptr(out), _ptr(request_of_row),
               _ptr(q_start), _ptr(q_len), _ptr(slots), T, int(num_requests), C, taps, 1 if silu else 0,
               1 if update_state else 0, _stream()), "short_conv")
     if update_state and taps > 1:
@@ -1241,9 +1245,13 @@ LATENT_TILE = 16     # packed rows (row x head) a block of the latent attention 
 LATENT_FMA = os.environ.get("PBE_LATENT", "").strip().lower() == "fma"
 
 
+LATENT_WIDE_TILE = 64    # packed rows a block takes in steps with prompt portions (four groups of 16)
+
+
 def latent_tile_rows(num_heads: int) -> int:
-    """Packed rows of a row tile of the work list: all heads of a row lie in one tile."""
-    return LATENT_TILE * ((num_heads + LATENT_TILE - 1) // LATENT_TILE)
+    """Packed rows of a row tile of the work list: all heads of a row lie in one tile, and a tile
+    is whole blocks of either size."""
+    return LATENT_WIDE_TILE * ((num_heads + LATENT_WIDE_TILE - 1) // LATENT_WIDE_TILE)
 
 
 def latent_prepare(proj: torch.Tensor, q_off: int, q_rank: int, c_off: int, rank: int, r_off: int, rot: int,
@@ -1338,7 +1346,7 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, sink: Optional[torch.
     fn = _fn("latent_attention", "pbe_latent_attention",
              [ctypes.POINTER(AttnParams), c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(ctypes.byref(p), _ptr(sink), dk, int(value_width), int(meta.num_work), _dtype_code(cache),
-              0 if LATENT_FMA else 1, _stream()), "latent_attention")
+              0 if LATENT_FMA else (1 if meta.decode_rows > 0 else 2), _stream()), "latent_attention")
     if meta.num_split_rows > 0:
         mp = AttnMergeParams(part_o=part_o.data_ptr(), part_ml=part_ml.data_ptr(), out=out.data_ptr(),
                              split_tokens=meta.split_tokens.data_ptr(), split_counts=meta.split_counts.data_ptr(),

@@ -77,6 +77,7 @@ class SelectiveStateSpace(Mixer):
         self.w_in = tensors.pop(prefix + n["inp"]).contiguous()
         self.w_o = tensors.pop(prefix + n["o"]).contiguous()
         self.conv_w, self.conv_b = f32("conv"), f32("conv_bias")
+        self.conv_wt = self.conv_w.t().contiguous()        # [taps, C]: the layout the eight-channel kernel reads
         self.dt_bias, self.a_log, self.skip, self.gain = f32("dt_bias"), f32("a_log"), f32("skip"), f32("norm")
 
     def chunk_rows(self, rows: int) -> int:
@@ -99,7 +100,8 @@ class SelectiveStateSpace(Mixer):
         else:
             conv_state = torch.empty((1, 0, C), dtype=torch.float32, device=x.device)
         xbc = ops.short_conv(xbc_in, self.conv_w, self.conv_b, conv_state, ctx.request_of_row, ctx.q_start, ctx.q_len,
-                             ctx.state_slots, ctx.num_requests, silu=True, update_state=cache.writes)
+                             ctx.state_slots, ctx.num_requests, silu=True, update_state=cache.writes,
+                             weight_t=self.conv_wt)
         dt, decay = ops.step_sizes(dt_in, self.dt_bias, self.a_log)
         xs, B, Cm = xbc[:, :inner], xbc[:, inner:inner + G * N], xbc[:, inner + G * N:]
         plan = None if getattr(ctx, "captured", False) else ctx.recurrence_plan(self.chunk_rows(ctx.num_tokens))

@@ -88,7 +88,8 @@ def test_short_convolution_carries_its_last_inputs(taps, C, dt):
     slots = [3, 0, 4]
     state[slots] = 0
     rows = i32([0] * 11 + [1] + [2] * 25)
-    got = ops.short_conv(dev, w.to(DEV), b.to(DEV), state, rows, i32([0, 11, 12]), i32(lens), i32(slots), 3)
+    got = ops.short_conv(dev, w.to(DEV), b.to(DEV), state, rows, i32([0, 11, 12]), i32(lens), i32(slots), 3,
+                         weight_t=w.t().contiguous().to(DEV))
     assert torch.allclose(got.float().cpu().double(), want, atol=tol, rtol=tol)
     # the third request again, in pieces, in the row the first one used
     state[3] = 0
