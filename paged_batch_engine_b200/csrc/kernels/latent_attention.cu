@@ -182,6 +182,8 @@ struct LatentAttnParams {
                              // num_kv_heads 1, tile_rows a multiple of 16
   const float* sink;         // [H] or null
   int dk, dv;                // width of a cache row; its leading dv values are the value
+  int sub;                   // blocks (along z) that share a key split of a split row, each an equal part of
+                             // its keys and a partial result of its own: slot split * sub + z of max_splits * sub
 };
 
 constexpr int LA_BM = 16;    // packed rows (row x head) a block
@@ -405,11 +407,15 @@ __global__ void __launch_bounds__(LM_WARPS * 32 * RG) latent_attention_mma_kerne
   const int hi_key = pos0 + row_hi + 1;
   const int lo_key = p.window > 0 ? max(0, pos0 + row_lo - p.window + 1) : 0;
   int k_begin = lo_key, k_end = hi_key;
+  const int Z = lp.sub, z = blockIdx.z;
   if (nsplit > 1) {
     const int lo_req = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int s0 = lo_req / p.split_keys;
-    k_begin = max(lo_key, (s0 + split) * p.split_keys);
-    k_end = min(hi_key, (s0 + split + 1) * p.split_keys);
+    const int part = p.split_keys / Z;              // a multiple of the key tile (the launcher checks)
+    k_begin = max(lo_key, (s0 + split) * p.split_keys + z * part);
+    k_end = min(hi_key, (s0 + split) * p.split_keys + (z + 1) * part);
+  } else if (z > 0) {
+    return;
   }
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = (tid >> 5) & 3, rg = tid >> 7;            // the warp's place in its group of four, and the group
@@ -418,15 +424,36 @@ __global__ void __launch_bounds__(LM_WARPS * 32 * RG) latent_attention_mma_kerne
   const __nv_bfloat16* kc = (const __nv_bfloat16*)p.k_cache;
   const int32_t* bt = p.block_table + (size_t)r * p.bt_stride;
 
-  for (int idx = tid; idx < ROWS * DK; idx += blockDim.x) {
-    const int i = idx / DK, d = idx - i * DK;
-    const int pr = pr0 + i;
-    float v = 0.f;
-    if (pr < n_packed) {
-      const int row = pr / G, hg = pr - row * G;
-      v = q[((size_t)(qs + row) * H + hg) * DK + d];
+  {
+    // the queries: 16-byte loads, four of a thread's in flight at once, rounded as they are staged
+    const int qchunks = DK / 4, total = ROWS * qchunks;
+    for (int first = 0; first < total; first += (int)blockDim.x * 4) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = first + tid + u * (int)blockDim.x;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < total) {
+          const int i = idx / qchunks, c = idx - i * qchunks;
+          const int pr = pr0 + i;
+          if (pr < n_packed) {
+            const int row = pr / G, hg = pr - row * G;
+            v[u] = *reinterpret_cast<const float4*>(q + ((size_t)(qs + row) * H + hg) * DK + c * 4);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = first + tid + u * (int)blockDim.x;
+        if (idx < total) {
+          const int i = idx / qchunks, c = idx - i * qchunks;
+          uint2 packed;
+          packed.x = pack_bf16(v[u].x, v[u].y);
+          packed.y = pack_bf16(v[u].z, v[u].w);
+          *reinterpret_cast<uint2*>(Qs + i * QSTR + c * 4) = packed;
+        }
+      }
     }
-    Qs[i * QSTR + d] = __float2bfloat16_rn(v);
   }
   // columns of the key tiles beyond the cached row (read as value columns that are never stored) stay zero
   for (int idx = tid; idx < 2 * LM_BN * (KSTR - DK); idx += blockDim.x) {
@@ -585,7 +612,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32 * RG) latent_attention_mma_kerne
       }
     } else {
       const int srow = p.tok_split_row[t];
-      const size_t base = ((size_t)srow * H + head) * p.max_splits + split;
+      const size_t base = ((size_t)srow * H + head) * (p.max_splits * Z) + split * Z + z;
       float* po = p.part_o + base * DV;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -612,7 +639,7 @@ int launch_latent_mma(const LatentAttnParams& lp, int num_work, cudaStream_t str
     cudaFuncSetAttribute(latent_attention_mma_kernel<NT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     opted = 200 * 1024;
   }
-  dim3 grid(num_work, (lp.a.tile_rows + ROWS - 1) / ROWS);
+  dim3 grid(num_work, (lp.a.tile_rows + ROWS - 1) / ROWS, lp.sub);
   launch_k(latent_attention_mma_kernel<NT, RG>, grid, LM_WARPS * 32 * RG, smem, stream, lp);
   return launch_status();
 }
@@ -635,35 +662,53 @@ int dispatch_latent_mma(const LatentAttnParams& lp, int num_work, bool wide_bloc
 }
 
 struct LatentMergeParams {
-  AttnMergeParams m;         // out: float32 [T, H, head_dim]
+  AttnMergeParams m;         // out: float32 [T, H, head_dim]; max_splits counts every partial slot of a row and head
   const float* sink;
+  int sub;                   // partial results per key split
 };
 
 __global__ void latent_merge_kernel(LatentMergeParams lp) {
+  extern __shared__ float weight[];        // [slots]: exp(m_s - m) of every partial result
+  __shared__ float red[33];
   const AttnMergeParams& p = lp.m;
   pdl_launch_dependents();
   pdl_wait();
   const int srow = blockIdx.x, head = blockIdx.y;
-  const int n = p.split_counts[srow];
-  if (n <= 1) return;
+  if (p.split_counts[srow] <= 1) return;
+  const int n = p.split_counts[srow] * lp.sub;
   const int t = p.split_tokens[srow];
   const size_t base = ((size_t)srow * p.num_heads + head) * p.max_splits;
+  // the partial results' maxima and sums are fetched side by side, one a thread
+  float m_mine = -INFINITY;
+  for (int s0 = threadIdx.x; s0 < n; s0 += blockDim.x) m_mine = fmaxf(m_mine, p.part_ml[(base + s0) * 2]);
+  m_mine = warp_max(m_mine);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m_mine;
+  __syncthreads();
   float m = lp.sink ? lp.sink[head] : -INFINITY;
-  for (int s = 0; s < n; ++s) m = fmaxf(m, p.part_ml[(base + s) * 2]);
-  float l = lp.sink ? expf(lp.sink[head] - m) : 0.f;
-  for (int s = 0; s < n; ++s) {
-    const float ms = p.part_ml[(base + s) * 2];
-    if (ms != -INFINITY) l += p.part_ml[(base + s) * 2 + 1] * expf(ms - m);
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) m = fmaxf(m, red[w]);
+  float l_mine = 0.f;
+  for (int s0 = threadIdx.x; s0 < n; s0 += blockDim.x) {
+    const float ms = p.part_ml[(base + s0) * 2];
+    const float w = ms == -INFINITY ? 0.f : expf(ms - m);
+    weight[s0] = w;
+    l_mine += w * p.part_ml[(base + s0) * 2 + 1];
   }
+  const float l = block_sum(l_mine, red) + (lp.sink ? expf(lp.sink[head] - m) : 0.f);   // also publishes weight[]
   const float inv = l > 0.f ? 1.0f / l : 0.f;
   float* o = (float*)p.out + ((size_t)t * p.num_heads + head) * p.head_dim;
+  const float* po = p.part_o + base * p.head_dim;
   for (int d = threadIdx.x; d < p.head_dim; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < n; ++s) {
-      const float ms = p.part_ml[(base + s) * 2];
-      if (ms != -INFINITY) a += p.part_o[(base + s) * p.head_dim + d] * expf(ms - m);
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    int s0 = 0;
+    for (; s0 + 8 <= n; s0 += 8) {         // eight loads in flight; the order of the sum is fixed by n alone
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = po[(size_t)(s0 + u) * p.head_dim + d];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a[u] = fmaf(v[u], weight[s0 + u], a[u]);
     }
-    o[d] = a * inv;
+    for (; s0 < n; ++s0) a[0] = fmaf(po[(size_t)s0 * p.head_dim + d], weight[s0], a[0]);
+    o[d] = (((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]))) * inv;
   }
 }
 
@@ -730,21 +775,27 @@ PBE_EXPORT int pbe_head_product(const void* a, int lda, int ha, int a_dtype, con
 
 // tensor_cores: bfloat16 caches with rows a multiple of 16 values wide take the mma.sync kernel
 // (1: blocks of 16 rows, for decoded tokens; 2: blocks of 64 rows, for prompt portions)
+// sub: blocks that share a key split (tensor-core kernel only; the partial buffers then hold max_splits * sub slots)
 PBE_EXPORT int pbe_latent_attention(const AttnParams* params, const float* sink, int dk, int dv, int num_work,
-                                    int cache_dtype, int tensor_cores, cudaStream_t stream) {
+                                    int cache_dtype, int tensor_cores, int sub, cudaStream_t stream) {
   if (num_work <= 0) return 0;
-  LatentAttnParams lp{*params, sink, dk, dv};
+  LatentAttnParams lp{*params, sink, dk, dv, sub < 1 ? 1 : sub};
   if (lp.a.tile_rows % LA_BM != 0 || lp.a.split_keys % LA_BN != 0 || dv > dk) return (int)cudaErrorInvalidValue;
-  if (tensor_cores && cache_dtype == PBE_BF16 && dk % 16 == 0)
-    return dispatch_latent_mma(lp, num_work, tensor_cores == 2, stream);
+  const bool mma = tensor_cores && cache_dtype == PBE_BF16 && dk % 16 == 0;
+  if (lp.sub > 1 && (!mma || lp.a.split_keys % (lp.sub * LM_BN) != 0)) return (int)cudaErrorInvalidValue;
+  if (mma) return dispatch_latent_mma(lp, num_work, tensor_cores == 2, stream);
   return cache_dtype == PBE_F32 ? dispatch_latent<float>(lp, num_work, stream)
                                 : dispatch_latent<__nv_bfloat16>(lp, num_work, stream);
 }
 
-PBE_EXPORT int pbe_latent_merge(const AttnMergeParams* params, const float* sink, int split_rows, cudaStream_t stream) {
+PBE_EXPORT int pbe_latent_merge(const AttnMergeParams* params, const float* sink, int sub, int split_rows,
+                                cudaStream_t stream) {
   if (split_rows <= 0) return 0;
-  LatentMergeParams lp{*params, sink};
+  LatentMergeParams lp{*params, sink, sub < 1 ? 1 : sub};
   dim3 grid(split_rows, lp.m.num_heads);
-  launch_k(latent_merge_kernel, grid, lp.m.head_dim >= 128 ? 128 : 64, 0, stream, lp);
+  const size_t smem = sizeof(float) * (size_t)lp.m.max_splits;
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  const int threads = lp.m.head_dim > 256 ? 512 : (lp.m.head_dim > 128 ? 256 : (lp.m.head_dim > 64 ? 128 : 64));
+  launch_k(latent_merge_kernel, grid, threads, smem, stream, lp);
   return launch_status();
 }

@@ -1243,6 +1243,7 @@ LATENT_TILE = 16     # packed rows (row x head) a block of the latent attention 
 # bfloat16 caches whose rows are a multiple of 16 values wide run on the tensor-core kernel;
 # PBE_LATENT=fma keeps them on the float32-arithmetic kernel (which every other case takes)
 LATENT_FMA = os.environ.get("PBE_LATENT", "").strip().lower() == "fma"
+LATENT_SUB = max(1, int(os.environ.get("PBE_LATENT_SUB", "4")))     # blocks that share a key split of a decode step
 
 
 LATENT_WIDE_TILE = 64    # packed rows a block takes in steps with prompt portions (four groups of 16)
@@ -1326,13 +1327,17 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, sink: Optional[torch.
     if (dk * 16 + (dk | 1) * 32) * 4 > 200 * 1024:
         raise KernelError(f"latent_attention: cached rows of {dk} values do not fit in shared memory")
     out = torch.empty((T, H, value_width), dtype=torch.float32, device=q.device)
+    mode = 0 if (LATENT_FMA or cache.dtype != torch.bfloat16 or dk % 16) else (1 if meta.decode_rows > 0 else 2)
+    # steps of decoded tokens in which every row's keys are split: four blocks share each split, so
+    # that few long requests still fill the GPU (8 requests at 2,048 keys: 64 -> 256 blocks)
+    sub = LATENT_SUB if (mode == 1 and meta.num_split_rows == T and meta.split_keys % (LATENT_SUB * 32) == 0) else 1
+    slots = meta.max_splits * sub
     part_o = part_ml = None
     if meta.num_split_rows:
         part_o, part_ml = meta.part_o, meta.part_ml       # the step's buffers, when they have this shape
-        if part_o is None or tuple(part_o.shape) != (meta.num_split_rows, H, meta.max_splits, value_width):
-            part_o = torch.empty((meta.num_split_rows, H, meta.max_splits, value_width), dtype=torch.float32,
-                                 device=q.device)
-            part_ml = torch.empty((meta.num_split_rows, H, meta.max_splits, 2), dtype=torch.float32, device=q.device)
+        if part_o is None or tuple(part_o.shape) != (meta.num_split_rows, H, slots, value_width):
+            part_o = torch.empty((meta.num_split_rows, H, slots, value_width), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((meta.num_split_rows, H, slots, 2), dtype=torch.float32, device=q.device)
     p = AttnParams(
         q=q.data_ptr(), k_cache=cache.data_ptr(), v_cache=cache.data_ptr(), out=out.data_ptr(),
         part_o=part_o.data_ptr() if part_o is not None else None,
@@ -1344,15 +1349,16 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, sink: Optional[torch.
         window=int(window or 0), split_keys=int(meta.split_keys), max_splits=int(meta.max_splits),
         tile_rows=int(meta.tile_rows), scale=float(scale), kinds=0, num_pages=int(cache.shape[0]))
     fn = _fn("latent_attention", "pbe_latent_attention",
-             [ctypes.POINTER(AttnParams), c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+             [ctypes.POINTER(AttnParams), c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(ctypes.byref(p), _ptr(sink), dk, int(value_width), int(meta.num_work), _dtype_code(cache),
-              0 if LATENT_FMA else (1 if meta.decode_rows > 0 else 2), _stream()), "latent_attention")
+              mode, sub, _stream()), "latent_attention")
     if meta.num_split_rows > 0:
         mp = AttnMergeParams(part_o=part_o.data_ptr(), part_ml=part_ml.data_ptr(), out=out.data_ptr(),
                              split_tokens=meta.split_tokens.data_ptr(), split_counts=meta.split_counts.data_ptr(),
-                             num_heads=int(H), head_dim=int(value_width), max_splits=int(meta.max_splits))
-        mfn = _fn("latent_attention", "pbe_latent_merge", [ctypes.POINTER(AttnMergeParams), c_void_p, c_int, c_void_p])
-        _check(mfn(ctypes.byref(mp), _ptr(sink), int(meta.num_split_rows), _stream()), "latent_merge")
+                             num_heads=int(H), head_dim=int(value_width), max_splits=int(slots))
+        mfn = _fn("latent_attention", "pbe_latent_merge", [ctypes.POINTER(AttnMergeParams), c_void_p, c_int, c_int,
+                                                           c_void_p])
+        _check(mfn(ctypes.byref(mp), _ptr(sink), sub, int(meta.num_split_rows), _stream()), "latent_merge")
     return out
 
 
