@@ -507,19 +507,28 @@ __global__ void __launch_bounds__(LM_WARPS * 32 * RG) latent_attention_mma_kerne
     __syncthreads();
     {
       // scores of the 16 rows against this warp's eight keys
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
-      const __nv_bfloat16* qa = Qs + (rg * LA_BM + g8) * QSTR + q2;
-      const __nv_bfloat16* kb = Ks + (warp * 8 + g8) * KSTR + q2;
-      for (int kk = 0; kk < DK; kk += 16) {
-        unsigned a[4];
-        a[0] = *reinterpret_cast<const unsigned*>(qa + kk);
-        a[1] = *reinterpret_cast<const unsigned*>(qa + 8 * QSTR + kk);
-        a[2] = *reinterpret_cast<const unsigned*>(qa + kk + 8);
-        a[3] = *reinterpret_cast<const unsigned*>(qa + 8 * QSTR + kk + 8);
-        const unsigned b0 = *reinterpret_cast<const unsigned*>(kb + kk);
-        const unsigned b1 = *reinterpret_cast<const unsigned*>(kb + kk + 8);
-        mma_bf16(c, a, b0, b1);
+      // two sums in turn, so that a product need not wait for the one before it; fragments by ldmatrix
+      // (a 16 x 16 piece of the queries, an 8 x 16 piece of the keys, one instruction each)
+      float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* qa = Qs + (rg * LA_BM + (lane & 7) + ((lane >> 3) & 1) * 8) * QSTR + (lane >> 4) * 8;
+      const __nv_bfloat16* kb = Ks + (warp * 8 + (lane & 7)) * KSTR + ((lane >> 3) & 1) * 8;
+      auto step = [&](int kk, float (&sum)[4]) {
+        unsigned a[4], b0, b1;
+        const unsigned qaddr = (unsigned)__cvta_generic_to_shared(qa + kk);
+        const unsigned kaddr = (unsigned)__cvta_generic_to_shared(kb + kk);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(qaddr));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(kaddr));
+        mma_bf16(sum, a, b0, b1);
+      };
+      int kk = 0;
+      for (; kk + 32 <= DK; kk += 32) {
+        step(kk, c);
+        step(kk + 16, c2);
       }
+      if (kk < DK) step(kk, c);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[i] += c2[i];
       float* s0 = Ss + (rg * LA_BM + g8) * (LM_BN + 1) + warp * 8 + q2;
       s0[0] = c[0]; s0[1] = c[1];
       s0[8 * (LM_BN + 1)] = c[2]; s0[8 * (LM_BN + 1) + 1] = c[3];
