@@ -239,3 +239,12 @@ def make_bavetar_folder(path, cfg: dict, seed: int, dtype=torch.bfloat16) -> str
         w[k] = t.to(w[k].dtype)
     save_file(w, f)
     return str(path)
+# one kind of layer only: a model without any paged cache, and one without any state row
+BAV_STATE_ONLY = dict(
+    architecture="Bavetar", width=48, vocab=150, norm=dict(eps=1e-5), logit_scale=1.5, logit_softcap=20.0,
+    layers=[dict(type="mamba2", mixer=_ssm(3, 8, 12, 3, 2, 3), mlp=dict(kind="dense", ff=40)),
+            dict(type="mamba2", mixer=_ssm(2, 16, 20, 1, 5, 1), mlp=None)])
+BAV_LATENT_ONLY = dict(
+    architecture="Bavetar", width=56, vocab=170, norm=dict(eps=1e-5), logit_scale=1.0, logit_softcap=12.0,
+    layers=[dict(type="latent_attention", mixer=_lat(2, 12, 6, 6, 20, 26, 10, 3000.0, 0.2), mlp=None),
+            dict(type="latent_attention", mixer=_lat(5, 8, 8, 8, 8, 16, 12, 3000.0, 0.3), mlp=_moe(16, 4, 2, 2, 1, 1.0))])

@@ -415,6 +415,21 @@ def test_schedules_agree_with_plain(folders, name, dtype):
             assert runner.cache.num_free_pages(gi) == runner.cache.pools[gi].num_pages
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["state", "latent"])
+def test_models_of_one_kind_of_layer(tmp_path, which, dtype):
+    """A model with state rows and no paged cache at all, and one with pages and no state row."""
+    from tests.helpers import BAV_LATENT_ONLY, BAV_STATE_ONLY
+    cfg = BAV_STATE_ONLY if which == "state" else BAV_LATENT_ONLY
+    folder = make_bavetar_folder(tmp_path / which, cfg, 31)
+    g = torch.Generator().manual_seed(4)
+    reqs = {f"q{i}": torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for i, n in enumerate([37, 5, 70])}
+    want = plain_logits(folder, reqs)
+    for label, recs in (("tail", ru.tail_decoded(reqs, 20)), ("mixed", ru.mixed(reqs, max_live=2, seed=3))):
+        runner = make_runner(folder, dtype, 8, ru.pool_tokens_needed(recs), max_requests=2)
+        check(ru.run_records(runner, recs), want, dtype, f"{which}/{label}")
+
+
 def test_batch_of_unequal_requests_equals_each_alone_and_slots_are_used_again(folders):
     """Eight requests through two request slots, two at a time, against each alone: a state row
     or a page that kept something of its former owner would show."""
