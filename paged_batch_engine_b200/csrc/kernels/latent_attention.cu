@@ -587,13 +587,22 @@ __global__ void __launch_bounds__(LM_WARPS * 32 * RG) latent_attention_mma_kerne
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const __nv_bfloat16* vrow = Ks + (16 * j + (lane & 15)) * KSTR + col0;
+      // four column tiles at a time: their products with the weights' first terms, then with the
+      // second terms, so that no product waits for the one issued just before it
+      constexpr int GRP = NT < 4 ? NT : 4;
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        unsigned b0, b1;
-        const unsigned addr = (unsigned)__cvta_generic_to_shared(vrow + nt * 8);
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
-        mma_bf16(acc[nt], a_hi[j], b0, b1);
-        mma_bf16(acc[nt], a_lo[j], b0, b1);
+      for (int nt0 = 0; nt0 < NT; nt0 += GRP) {
+        unsigned b[GRP][2];
+#pragma unroll
+        for (int u = 0; u < GRP; ++u) {
+          const unsigned addr = (unsigned)__cvta_generic_to_shared(vrow + (nt0 + u) * 8);
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                       : "=r"(b[u][0]), "=r"(b[u][1]) : "r"(addr));
+        }
+#pragma unroll
+        for (int u = 0; u < GRP; ++u) mma_bf16(acc[nt0 + u], a_hi[j], b[u][0], b[u][1]);
+#pragma unroll
+        for (int u = 0; u < GRP; ++u) mma_bf16(acc[nt0 + u], a_lo[j], b[u][0], b[u][1]);
       }
     }
   }
