@@ -296,7 +296,8 @@ def test_latent_attention_with_a_stand_out_key_and_a_sink(H, D, R, rot_dims, V, 
     sink = torch.linspace(-6.0, 9.0, H)
     part, m, w = _latent_part(H, D, R, rot_dims, V, rank, q_rank, hidden, dtype, T + H, sink)
     g = torch.Generator().manual_seed(T)
-    marks = sorted({0, 1, page - 1, page, 2 * page - 1, T // 2, T - 20, T - 2} & set(range(T)))
+    # 511, 512: where the keys of a long request are split over blocks
+    marks = sorted({0, 1, page - 1, page, 2 * page - 1, 511, 512, T // 2, T - 20, T - 2} & set(range(T)))
     for mark in marks[:: (1 if dtype == torch.float32 and T < 500 else 3)]:
         x = torch.randn(T, hidden, generator=g) * 0.5
         x[:, 0] = 3.0                      # every query looks along the key's last value
